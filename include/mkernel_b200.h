@@ -1,0 +1,154 @@
+/*
+ * mkernel_b200 -- C ABI of the B200 (sm_100a) tensor-parallel GEMM + collective operators.
+ *
+ * This is the boundary a host language binds (ctypes, cgo, JNI, pybind).  Every entry point takes
+ * plain pointers and sizes, returns 0 on success or a negative mk_status, never exits the
+ * process and never throws.  mk_last_error() returns a thread-local message for the last failure.
+ *
+ * One process drives one GPU.  "Symmetric" buffers are allocated collectively by all ranks of a
+ * node, each rank holding its own copy plus mapped addresses of every peer's copy and, when
+ * requested and supported, one NVSwitch multicast address that aliases all copies.
+ *
+ * Each operator entry below names the reference interface it stands in for
+ * (paths inside uccl-project/mKernel).
+ */
+#ifndef MKERNEL_B200_H_
+#define MKERNEL_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MK_MAX_WORLD 8
+
+typedef enum mk_status {
+  MK_OK = 0,
+  MK_ERR_INVALID = -1,      /* bad argument / unsupported shape (reference: TORCH_CHECK failure) */
+  MK_ERR_CUDA = -2,         /* a CUDA runtime or driver call failed */
+  MK_ERR_TRANSPORT = -3,    /* rendezvous between ranks failed or timed out */
+  MK_ERR_UNSUPPORTED = -4,  /* feature not available on this system (e.g. multicast) */
+  MK_ERR_DEVICE_WAIT = -5   /* a device-side bounded wait expired (see mk_op_status) */
+} mk_status;
+
+/* Layout of operand B. */
+#define MK_B_NK 0 /* B stored [N, K], K contiguous (AllGather+GEMM, GEMM+ReduceScatter) */
+#define MK_B_KN 1 /* B stored [K, N], N contiguous (GEMM+AllReduce) */
+
+typedef struct mk_comm mk_comm; /* per-process rendezvous + device context           */
+typedef struct mk_symm mk_symm; /* one symmetric allocation                          */
+
+/* View of a symmetric allocation that the operators consume.  A caller with its own symmetric
+ * heap can fill this struct by hand instead of using mk_symm_alloc. */
+typedef struct mk_symm_view {
+  int rank;
+  int world;
+  size_t bytes;
+  void* peer[MK_MAX_WORLD]; /* peer[rank] is the local copy */
+  void* mc;                 /* multicast alias or NULL */
+} mk_symm_view;
+
+const char* mk_last_error(void);
+int mk_version(void);
+
+/* ---- transport: replaces include/comm/local_broker.cuh:362-534 (shm + unix-socket broker),
+ *      include/comm/ipc.cuh:100-122 (fd import) and include/comm/vmm.cuh:29-119 (VMM, multicast).
+ * `key` names the rendezvous; all ranks of one job pass the same key.  Collective calls must be
+ * made by every rank in the same order. */
+int mk_comm_create(const char* key, int rank, int world, int device, mk_comm** out);
+int mk_comm_destroy(mk_comm* comm);
+int mk_comm_rank(const mk_comm* comm);
+int mk_comm_world(const mk_comm* comm);
+int mk_comm_barrier(mk_comm* comm);
+/* Every rank contributes `bytes` (<= 256) bytes; out receives world * bytes. */
+int mk_comm_allgather(mk_comm* comm, const void* in, size_t bytes, void* out);
+/* Every rank contributes one file descriptor; out_fds[r] is a descriptor in this process that
+ * refers to rank r's file (out_fds[rank] is a dup of fd).  The caller closes them. */
+int mk_comm_allgather_fd(mk_comm* comm, int fd, int* out_fds);
+
+/* ---- symmetric memory: replaces dist::ParallelBuffer, include/dist/parallel_buffer.cuh:87-338 */
+int mk_symm_alloc(mk_comm* comm, size_t bytes, int want_multicast, mk_symm** out);
+int mk_symm_free(mk_symm* buf);
+int mk_symm_get_view(const mk_symm* buf, mk_symm_view* out);
+
+/* ---- operators.  `stream` is a cudaStream_t.  All launches are asynchronous. ---------------- */
+
+/* Words (uint32) an operator's synchronisation buffer must hold.  The buffers are symmetric,
+ * multicast not required, and must be zeroed once (see the *_prepare calls).
+ * Reference: ag_gemm_warp_specialized_ready_words, gemm_rs_blackwell_sync_shape
+ * (include/operators/ag_gemm/ag_gemm_warp_specialized_session.cuh:12-47,
+ *  include/operators/gemm_rs/gemm_rs_blackwell_session.cuh:11-15), barrier (2,1024,1024). */
+#define MK_AG_READY_WORDS 65536
+#define MK_RS_SYNC_WORDS 524288
+#define MK_AR_BARRIER_WORDS (2 * 1024 * 1024)
+
+/* Plain C[M,N] = A[M,K] * B on one GPU (bf16 in, fp32 accumulate, bf16 out).  The W = 1 case of
+ * every fused operator; no counterpart entry point in the reference.  `status4` may be NULL or
+ * point to 4 zeroed device words that receive a failure record. */
+int mk_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int b_layout,
+                 uint32_t* status4, void* stream);
+
+/* AllGather + GEMM.  Replaces ag_gemm_warp_specialized_prepare / _launch
+ * (include/operators/ag_gemm/ag_gemm_warp_specialized.cuh:331-406,
+ *  src/ag_gemm_warp_specialized.cu:115-134, 610-696).
+ * A: symmetric [W, M/W, K] bf16, rank r has filled slab r.  ready: symmetric MK_AG_READY_WORDS.
+ * B: [N, K] bf16.  C: [W, M/W, N] bf16 (M = total rows).  prepare is the all-rank entry barrier
+ * and must precede every launch on the same stream. */
+int mk_ag_gemm_prepare(const mk_symm_view* ready, void* stream);
+int mk_ag_gemm_launch(const mk_symm_view* A, const mk_symm_view* ready, const void* B, void* C,
+                      int M, int N, int K, void* stream);
+
+/* GEMM + ReduceScatter.  Replaces gemm_rs_blackwell_prepare / _launch
+ * (src/gemm_rs_blackwell.cu:642-732).  A: [M, K_local], B: [N, K_local], C: symmetric [M, N]
+ * (receives the partial product, then rows [rank*M/W, (rank+1)*M/W) are overwritten with the
+ * reduced result).  sync: symmetric MK_RS_SYNC_WORDS.  prepare zeroes sync once; the caller
+ * then synchronises the stream and barriers all ranks before the first launch. */
+int mk_gemm_rs_prepare(const mk_symm_view* sync, void* stream);
+int mk_gemm_rs_launch(const void* A, const void* B, const mk_symm_view* C,
+                      const mk_symm_view* sync, int M, int N, int K, void* stream);
+
+/* GEMM + AllReduce.  Replaces gemm_ar_intranode_blackwell
+ * (include/operators/gemm_ar/gemm_ar_blackwell.cuh:205-246, src/gemm_ar_blackwell.cu:57-610).
+ * A: [M, K_local], B: [K_local, N] (MK_B_KN) or [N, K_local] (MK_B_NK).  C: symmetric [M, N]
+ * partial product.  C_final: symmetric [M, N], complete on every rank when the launch ends.
+ * barrier: symmetric MK_AR_BARRIER_WORDS, zeroed once.  epoch: strictly increasing from 1. */
+int mk_gemm_ar_launch(const void* A, const void* B, const mk_symm_view* C,
+                      const mk_symm_view* barrier, const mk_symm_view* C_final, int M, int N,
+                      int K, uint32_t epoch, int b_layout, void* stream);
+
+/* Reads the 4 status words {code, where, detail0, detail1} of an operator's synchronisation
+ * buffer (synchronous device-to-host copy).  Returns MK_ERR_DEVICE_WAIT when code != 0. */
+int mk_op_status(const mk_symm_view* sync, uint32_t out4[4]);
+/* Clears the status words (asynchronous memset on `stream`). */
+int mk_op_status_clear(const mk_symm_view* sync, void* stream);
+
+/* ---- options (process-wide): "wait_limit_ms" (device wait budget, default 4000),
+ *      "n_comm" (exchange CTAs, 0 = heuristic), "block_n" (0 = heuristic), "group_rows",
+ *      "use_nvls" (0/1: reduce through NVSwitch multicast when the buffers have an alias). */
+int mk_set_option(const char* name, long long value);
+long long mk_get_option(const char* name);
+
+/* ---- introspection used by host-side tests and tools (no GPU needed) ---------------------- */
+typedef struct mk_plan {
+  int block_n, stages, n_comm, grid, smem_bytes;
+  int row_blocks, col_blocks, k_blocks, part_rows, part_blocks, interleave, group_rows;
+  long long sync_words;
+} mk_plan;
+/* Launch plan for op (0 GEMM, 1 AG, 2 RS, 3 AR) without touching a device; num_sms <= 0 means
+ * 148. */
+int mk_plan_op(int op, int rank, int world, int M, int N, int K, int b_layout, int num_sms,
+               mk_plan* out);
+/* Tile visiting order of a compute CTA set: writes row0/rows/col0 per tile, returns tile count
+ * (or a negative status).  `cap` is the capacity of each output array. */
+int mk_sched_tiles(int op, int rank, int world, int M, int N, int block_n, int group_rows,
+                   int* row0, int* rows, int* col0, int* rowblock, int cap);
+/* Rows [row0,row1) that owner `owner` reduces for its k-th item; returns number of items. */
+int mk_sched_owner_items(int op, int world, int M, int N, int block_n, int owner, int* row0,
+                         int* row1, int cap);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MKERNEL_B200_H_ */

@@ -1,0 +1,671 @@
+// One persistent sm_100a kernel for the tensor-parallel GEMM + collective operators.
+//
+// CTA roles (fixed for the lifetime of the kernel, chosen by blockIdx.x):
+//   exchange CTAs [0, n_comm)  AllGather: pull peers' A rows into the local gathered buffer with
+//                              untiled bulk copies (peer global -> shared -> local global) and raise
+//                              one flag per 16-row group.
+//                              ReduceScatter / AllReduce: wait until every rank has raised the
+//                              flags of a row-block this rank owns, sum the W partial copies
+//                              (fp32 accumulate, fixed rank order) and write the bf16 result
+//                              locally (RS) or to every rank's output (AR).
+//   compute CTAs  [n_comm, G)  bf16 GEMM tiles of 128 x block_n: warp 0 feeds a shared-memory ring
+//                              with TMA tile loads, warp 1 issues tcgen05.mma into one of two TMEM
+//                              accumulators, warps 4-7 drain the other accumulator (tcgen05.ld ->
+//                              bf16 -> global), warp 2 publishes finished tiles to their owners.
+//
+// Every wait is bounded: when a wait expires the CTA records {code, where, detail} in the status
+// words, raises an abort flag that all other waits observe, and the kernel drains and returns.
+//
+// Behaviour follows the reference operators (semantics only): AllGather+GEMM
+// src/ag_gemm_warp_specialized.cu:166-580, GEMM+ReduceScatter src/gemm_rs_blackwell.cu:374-615,
+// GEMM+AllReduce src/gemm_ar_blackwell.cu:57-610.
+#pragma once
+#include "op_params.h"
+#include "ptx.cuh"
+
+namespace mkb {
+
+// Barrier slots inside the CTA's barrier block (8 bytes each).
+enum BarSlot : int {
+  BAR_FULL = 0,      // [0,8)   operand stage filled by TMA           (compute CTAs)
+  BAR_EMPTY = 8,     // [8,16)  operand stage consumed by the MMAs
+  BAR_TFULL = 16,    // [16,18) accumulator ready for the epilogue
+  BAR_TEMPTY = 18,   // [18,20) accumulator drained
+  BAR_STORED = 20,   // [20,22) tile written to global memory by all four epilogue warps
+  BAR_SLOT = 0,      // [0,24)  ring slot filled                      (exchange CTAs)
+  BAR_COUNT = 32,
+};
+
+struct WaitCtx {
+  uint32_t* status;            // global status words (may be null)
+  volatile uint32_t* s_abort;  // CTA-wide abort flag in shared memory
+  uint64_t limit_ns;
+  uint32_t where;              // (blockIdx << 8) | role
+};
+
+__device__ __forceinline__ uint64_t global_timer_ns() {
+  uint64_t t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+
+__device__ __noinline__ void report_failure(const WaitCtx& c, int code, uint32_t d0, uint32_t d1) {
+  if (c.status != nullptr) {
+    if (atomicCAS(c.status, 0u, static_cast<uint32_t>(code)) == 0u) {
+      c.status[1] = c.where;
+      c.status[2] = d0;
+      c.status[3] = d1;
+      __threadfence();
+    }
+  }
+  *c.s_abort = 1u;
+}
+
+template <bool kSleep, class Pred>
+__device__ __noinline__ bool slow_wait(const WaitCtx& c, Pred pred, int code, uint32_t d0,
+                                       uint32_t d1) {
+  uint32_t it = 0;
+  uint64_t t0 = 0;
+  while (true) {
+    if (pred()) return true;
+    ++it;
+    if (kSleep && it > 16) __nanosleep(it > 2048 ? 400 : 40);
+    if ((it & 127u) == 0u) {
+      if (*c.s_abort != 0u) return false;
+      if (c.status != nullptr && ptx::ld_relaxed_sys(c.status) != 0u) {
+        *c.s_abort = 1u;
+        return false;
+      }
+      const uint64_t now = global_timer_ns();
+      if (t0 == 0) {
+        t0 = now;
+      } else if (now - t0 > c.limit_ns) {
+        report_failure(c, code, d0, d1);
+        return false;
+      }
+    }
+  }
+}
+
+// Returns false when the wait expired or another role aborted.
+template <bool kSleep, class Pred>
+__device__ __forceinline__ bool bounded_wait(const WaitCtx& c, Pred pred, int code, uint32_t d0,
+                                             uint32_t d1) {
+  if (pred()) return true;
+  return slow_wait<kSleep>(c, pred, code, d0, d1);
+}
+
+__device__ __forceinline__ bool wait_mbar(const WaitCtx& c, uint32_t bar, uint32_t parity,
+                                          uint32_t d0) {
+  return bounded_wait<false>(c, [&] { return ptx::mbar_try_wait(bar, parity); },
+                             ST_TIMEOUT_PIPE, d0, parity);
+}
+
+struct TileInfo {
+  int rowblock, q, row0, rows, n0;
+};
+__device__ __forceinline__ TileInfo tile_info(const Sched& s, int t) {
+  TileInfo ti;
+  tile_to_coord(s, t, &ti.rowblock, &ti.q);
+  ti.row0 = rowblock_row0(s, ti.rowblock);
+  ti.rows = rowblock_rows(s, ti.rowblock);
+  ti.n0 = ti.q * s.block_n;
+  return ti;
+}
+
+// ------------------------------------------------------------------------------------------
+// Compute CTA
+// ------------------------------------------------------------------------------------------
+template <int OP>
+__device__ __forceinline__ void compute_cta(const CUtensorMap* tma_a, const CUtensorMap* tma_b,
+                                            const OpParams& p, uint32_t smem_base,
+                                            uint32_t bar_base, volatile uint32_t* s_tmem,
+                                            WaitCtx& wc, uint32_t epoch) {
+  const Sched& s = p.sched;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int cta = blockIdx.x - p.n_comm;
+  const int n_comp = gridDim.x - p.n_comm;
+  const int total = s.P * s.Q;
+  const int bn = s.block_n;
+  const int stage_sz = stage_bytes(bn);
+  const uint32_t tmem_base = *s_tmem;
+  auto bar = [&](int slot) { return bar_base + 8u * slot; };
+  constexpr bool kSignals = (OP == OP_RS || OP == OP_AR);
+
+  if (warp == 0) {
+    // ---------------- TMA producer ----------------
+    wc.where = (blockIdx.x << 8) | 0u;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    for (int t = cta; t < total && ok; t += n_comp) {
+      const TileInfo ti = tile_info(s, t);
+      if (OP == OP_AG && s.world > 1 && rowblock_shard(s, ti.rowblock) != s.rank) {
+        // Rows of a remote shard: wait until the exchange CTAs have landed all 16-row groups.
+        bool mine = true;
+        if (lane < kGatherSub) {
+          const uint32_t* f = p.sync + SW_FLAGS + gather_flag_index(ti.rowblock, lane);
+          mine = bounded_wait<true>(wc, [&] { return ptx::ld_acquire_gpu(f) == epoch; },
+                                    ST_TIMEOUT_GATHER, ti.rowblock, lane);
+        }
+        ok = __all_sync(0xffffffffu, mine);
+        ptx::fence_proxy_async();  // gathered rows were written through another proxy
+        if (!ok) break;
+      }
+      if (lane == 0) {
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!wait_mbar(wc, bar(BAR_EMPTY + stage), phase ^ 1u, 0x100u + stage)) { ok = false; break; }
+          const uint32_t a_dst = smem_base + stage * stage_sz;
+          const uint32_t b_dst = a_dst + kBlockM * kBlockK * 2;
+          ptx::mbar_expect_tx(bar(BAR_FULL + stage), stage_sz);
+          ptx::tma_load_2d(a_dst, tma_a, bar(BAR_FULL + stage), kb * kBlockK, ti.row0);
+          if (!p.b_mn_major) {
+            ptx::tma_load_2d(b_dst, tma_b, bar(BAR_FULL + stage), kb * kBlockK, ti.n0);
+          } else {
+            for (int c = 0; c < bn / 64; ++c)
+              ptx::tma_load_2d(b_dst + c * 8192, tma_b, bar(BAR_FULL + stage), ti.n0 + c * 64,
+                               kb * kBlockK);
+          }
+          if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+        }
+      }
+      ok = __all_sync(0xffffffffu, ok);
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (one thread) ----------------
+    wc.where = (blockIdx.x << 8) | 1u;
+    if (lane == 0) {
+      const uint32_t idesc = ptx::make_idesc_bf16(bn, p.b_mn_major);
+      int stage = 0, acc = 0;
+      uint32_t phase = 0, acc_phase = 0;
+      bool ok = true;
+      for (int t = cta; t < total && ok; t += n_comp) {
+        if (!wait_mbar(wc, bar(BAR_TEMPTY + acc), acc_phase ^ 1u, 0x200u + acc)) break;
+        ptx::tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * 256;
+        for (int kb = 0; kb < p.k_blocks; ++kb) {
+          if (!wait_mbar(wc, bar(BAR_FULL + stage), phase, 0x300u + stage)) { ok = false; break; }
+          ptx::tc_fence_after();
+          const uint32_t a_base = smem_base + stage * stage_sz;
+          const uint32_t b_base = a_base + kBlockM * kBlockK * 2;
+#pragma unroll
+          for (int k = 0; k < kBlockK / 16; ++k) {
+            // A: K-major, 128-byte swizzle: rows are 128 B apart, 8-row groups 1024 B apart;
+            // a K step of 16 elements moves the start address by 32 B inside the swizzle row.
+            const uint64_t a_desc = ptx::make_smem_desc_sw128(a_base + k * 32, 16, 1024);
+            // B: same layout when stored [N,K]; when stored [K,N] the tile is held as 64-column
+            // panels (8192 B apart) of 64 k-rows x 128 B, and a K step of 16 moves by 2048 B.
+            const uint64_t b_desc =
+                p.b_mn_major ? ptx::make_smem_desc_sw128(b_base + k * 2048, 8192, 1024)
+                             : ptx::make_smem_desc_sw128(b_base + k * 32, 16, 1024);
+            ptx::umma_bf16(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          ptx::umma_commit(bar(BAR_EMPTY + stage));  // stage reusable once these MMAs finish
+          if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+        }
+        if (!ok) break;
+        ptx::umma_commit(bar(BAR_TFULL + acc));      // accumulator complete
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else if (warp == 2) {
+    // ---------------- tile publisher (RS / AR) ----------------
+    wc.where = (blockIdx.x << 8) | 2u;
+    if (kSignals && s.world > 1 && lane == 0) {
+      int acc = 0;
+      uint32_t acc_phase = 0;
+      for (int t = cta; t < total; t += n_comp) {
+        const TileInfo ti = tile_info(s, t);
+        if (!wait_mbar(wc, bar(BAR_STORED + acc), acc_phase, 0x400u + acc)) break;
+        // The tile's rows are in this GPU's memory; make them visible system-wide, then tell
+        // every owner whose rows intersect the tile.
+        ptx::fence_acq_rel_sys();
+        int lo, hi;
+        rowblock_owners(s, ti.rowblock, &lo, &hi);
+        const long long idx = SW_FLAGS + tile_flag_index(s, s.rank, ti.rowblock, ti.q);
+        for (int o = lo; o <= hi; ++o) ptx::st_relaxed_sys(p.peer_sync[o] + idx, epoch);
+        ptx::mbar_arrive(bar(BAR_TEMPTY + acc));
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else if (warp >= 4) {
+    // ---------------- epilogue: TMEM -> registers -> bf16 -> global ----------------
+    wc.where = (blockIdx.x << 8) | 4u;
+    const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
+    int acc = 0;
+    uint32_t acc_phase = 0;
+    __nv_bfloat16* C = static_cast<__nv_bfloat16*>(p.C);
+    for (int t = cta; t < total; t += n_comp) {
+      const TileInfo ti = tile_info(s, t);
+      if (!wait_mbar(wc, bar(BAR_TFULL + acc), acc_phase, 0x500u + acc)) break;
+      ptx::tc_fence_after();
+      const int r_in_tile = quarter * 32 + lane;
+      const bool row_ok = r_in_tile < ti.rows;
+      __nv_bfloat16* crow = C + static_cast<long long>(ti.row0 + r_in_tile) * p.ldc;
+      const uint32_t t_base = tmem_base + acc * 256 + (static_cast<uint32_t>(quarter * 32) << 16);
+      for (int c = 0; c < bn; c += 32) {
+        uint32_t r[32];
+        ptx::tmem_ld_32x32(t_base + c, r);
+        ptx::tmem_ld_wait();
+        const int col = ti.n0 + c;
+        if (row_ok) {
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            if (col + g * 8 + 8 <= s.N) {
+              uint4 v;
+              v.x = ptx::pack_bf16x2(__uint_as_float(r[g * 8 + 0]), __uint_as_float(r[g * 8 + 1]));
+              v.y = ptx::pack_bf16x2(__uint_as_float(r[g * 8 + 2]), __uint_as_float(r[g * 8 + 3]));
+              v.z = ptx::pack_bf16x2(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5]));
+              v.w = ptx::pack_bf16x2(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7]));
+              ptx::st_global_v4(crow + col + g * 8, v);
+            }
+          }
+        }
+      }
+      ptx::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        ptx::mbar_arrive(bar(BAR_TEMPTY + acc));
+        if (kSignals && s.world > 1) ptx::mbar_arrive(bar(BAR_STORED + acc));
+      }
+      acc ^= 1;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Exchange CTA: AllGather pull
+// ------------------------------------------------------------------------------------------
+struct GatherCursor {
+  // Walks the 16-row groups assigned to this CTA and the 16 KiB chunks inside each group.
+  int x, x_end, stride;  // item index: ((d-1) * part_blocks + j) * kGatherSub + g
+  int chunk, n_chunks;
+  long long bytes, offset;  // of the current item inside the gathered buffer
+  int rowblock, sub;
+};
+
+__device__ __forceinline__ void gather_load_item(const OpParams& p, GatherCursor& c) {
+  const Sched& s = p.sched;
+  {
+    const int g = c.x % kGatherSub;
+    const int bj = c.x / kGatherSub;
+    const int d = 1 + bj / s.part_blocks, j = bj % s.part_blocks;
+    const int src = (s.rank + d) % s.world;
+    c.rowblock = src * s.part_blocks + j;
+    c.sub = g;
+    const int rows_in_block = rowblock_rows(s, c.rowblock);
+    const int r0 = g * (kBlockM / kGatherSub);
+    int r1 = r0 + kBlockM / kGatherSub;
+    if (r1 > rows_in_block) r1 = rows_in_block;
+    const int nrows = r1 > r0 ? r1 - r0 : 0;
+    c.bytes = static_cast<long long>(nrows) * p.K * 2;
+    c.offset = (static_cast<long long>(rowblock_row0(s, c.rowblock)) + r0) * p.K * 2;
+    c.n_chunks = static_cast<int>((c.bytes + kGatherChunk - 1) / kGatherChunk);
+    c.chunk = 0;
+  }
+}
+__device__ __forceinline__ bool gather_valid(const GatherCursor& c) { return c.x < c.x_end; }
+// Advance by one chunk; items without rows have n_chunks == 0 and are skipped by the caller.
+__device__ __forceinline__ void gather_advance(const OpParams& p, GatherCursor& c) {
+  if (++c.chunk >= c.n_chunks) {
+    c.x += c.stride;
+    if (c.x < c.x_end) gather_load_item(p, c);
+  }
+}
+
+__device__ __forceinline__ void gather_cta(const OpParams& p, uint32_t smem_base,
+                                           uint32_t bar_base, WaitCtx& wc, uint32_t epoch,
+                                           int ring_bytes) {
+  if (threadIdx.x != 0) return;
+  const Sched& s = p.sched;
+  wc.where = (blockIdx.x << 8) | 8u;
+  int ns = ring_bytes / kGatherChunk;
+  if (ns > 24) ns = 24;
+  auto bar = [&](int slot) { return bar_base + 8u * slot; };
+  const int n_items = (s.world - 1) * s.part_blocks * kGatherSub;
+
+  GatherCursor ld, st;
+  ld.x = blockIdx.x; ld.x_end = n_items; ld.stride = p.n_comm;
+  ld.n_chunks = 0; ld.chunk = 0;
+  if (gather_valid(ld)) gather_load_item(p, ld);
+  st = ld;
+  uint32_t* flags = p.sync + SW_FLAGS;
+
+  // Row groups that have no rows (ragged last block) are flagged straight away.
+  auto skip_empty = [&](GatherCursor& c, bool flag_it) {
+    while (gather_valid(c) && c.n_chunks == 0) {
+      if (flag_it) ptx::st_release_gpu(flags + gather_flag_index(c.rowblock, c.sub), epoch);
+      c.x += c.stride;
+      if (gather_valid(c)) gather_load_item(p, c);
+    }
+  };
+  skip_empty(ld, false);
+  skip_empty(st, true);
+
+  long long l = 0, sidx = 0;  // ring positions of the next load / next store
+  while (gather_valid(st)) {
+    while (gather_valid(ld) && l <= sidx - 2 + ns) {
+      const int slot = static_cast<int>(l % ns);
+      const long long off = ld.offset + static_cast<long long>(ld.chunk) * kGatherChunk;
+      long long nb = ld.bytes - static_cast<long long>(ld.chunk) * kGatherChunk;
+      if (nb > kGatherChunk) nb = kGatherChunk;
+      const int src = rowblock_shard(s, ld.rowblock);
+      ptx::mbar_expect_tx(bar(BAR_SLOT + slot), static_cast<uint32_t>(nb));
+      ptx::bulk_g2s(smem_base + slot * kGatherChunk,
+                    static_cast<const char*>(p.peer_data[src]) + off, static_cast<uint32_t>(nb),
+                    bar(BAR_SLOT + slot));
+      gather_advance(p, ld);
+      skip_empty(ld, false);
+      ++l;
+    }
+    const int slot = static_cast<int>(sidx % ns);
+    const uint32_t parity = static_cast<uint32_t>((sidx / ns) & 1);
+    if (!bounded_wait<false>(wc, [&] { return ptx::mbar_try_wait(bar(BAR_SLOT + slot), parity); },
+                             ST_TIMEOUT_COPY, st.rowblock, st.sub))
+      return;
+    const long long off = st.offset + static_cast<long long>(st.chunk) * kGatherChunk;
+    long long nb = st.bytes - static_cast<long long>(st.chunk) * kGatherChunk;
+    if (nb > kGatherChunk) nb = kGatherChunk;
+    ptx::bulk_s2g(static_cast<char*>(p.peer_data[s.rank]) + off, smem_base + slot * kGatherChunk,
+                  static_cast<uint32_t>(nb));
+    ptx::bulk_commit();
+    if (st.chunk + 1 >= st.n_chunks) {
+      // Last chunk of a 16-row group: wait until every store of the group has been written,
+      // then publish the group to the compute CTAs of this GPU.
+      ptx::bulk_wait_all<0>();
+      ptx::fence_proxy_async();
+      __threadfence();
+      ptx::st_release_gpu(flags + gather_flag_index(st.rowblock, st.sub), epoch);
+    } else {
+      ptx::bulk_wait_read<1>();
+    }
+    gather_advance(p, st);
+    skip_empty(st, true);
+    ++sidx;
+  }
+  ptx::bulk_wait_all<0>();
+}
+
+// ------------------------------------------------------------------------------------------
+// Exchange CTA: reduce (ReduceScatter / AllReduce)
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void accumulate_bf16x8(float (&acc)[8], const uint4& v) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    acc[2 * i + 0] += __uint_as_float(w[i] << 16);
+    acc[2 * i + 1] += __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+
+template <int OP>
+__device__ __forceinline__ void reduce_cta(const OpParams& p, uint32_t smem_base,
+                                           uint32_t bar_base, WaitCtx& wc, uint32_t epoch,
+                                           int ring_bytes) {
+  const Sched& s = p.sched;
+  const int tid = threadIdx.x;
+  const int W = s.world;
+  wc.where = (blockIdx.x << 8) | 9u;
+  auto bar = [&](int slot) { return bar_base + 8u * slot; };
+  const int set_bytes = W * kReduceChunk;
+  int ns = ring_bytes / set_bytes;
+  if (ns > 24) ns = 24;
+  const uint32_t* flags = p.sync + SW_FLAGS;
+  const int n_items = owner_num_items(s, s.rank);
+  const int first_block = owner_first_block(s, s.rank);
+  const long long row_bytes = static_cast<long long>(s.N) * 2;
+  const bool nvls = p.use_nvls && p.mc_data != nullptr && (OP == OP_RS || p.mc_out != nullptr);
+  long long pos = 0;  // ring position, continues across items
+
+  for (int k = 0; k < n_items; ++k) {
+    const int rb = first_block + k;
+    // 1. every rank must have published every column block of this row-block
+    {
+      bool ok = true;
+      for (int idx = tid; idx < W * s.Q && ok; idx += kThreads) {
+        const int src = idx / s.Q, q = idx % s.Q;
+        const uint32_t* f = flags + tile_flag_index(s, src, rb, q);
+        ok = bounded_wait<true>(wc, [&] { return ptx::ld_acquire_sys(f) == epoch; },
+                                ST_TIMEOUT_TILE, (src << 24) | rb, q);
+      }
+      __syncthreads();
+      if (*wc.s_abort != 0u) return;
+    }
+    int row0, row1;
+    owner_item_rows(s, s.rank, k, &row0, &row1);
+    const long long base = static_cast<long long>(row0) * row_bytes;
+    const long long bytes = static_cast<long long>(row1 - row0) * row_bytes;
+    const int n_chunks = static_cast<int>((bytes + kReduceChunk - 1) / kReduceChunk);
+    const int n_mine = n_chunks > static_cast<int>(blockIdx.x)
+                           ? (n_chunks - 1 - static_cast<int>(blockIdx.x)) / p.n_comm + 1 : 0;
+    auto chunk_off = [&](int i) {
+      return static_cast<long long>(blockIdx.x + static_cast<long long>(i) * p.n_comm) * kReduceChunk;
+    };
+    auto chunk_len = [&](int i) {
+      long long nb = bytes - chunk_off(i);
+      return static_cast<uint32_t>(nb > kReduceChunk ? kReduceChunk : nb);
+    };
+
+    if (nvls) {
+      // 2a. NVSwitch path: one multimem load returns the fp32-accumulated sum of all replicas.
+      for (int i0 = 0; i0 < n_mine; i0 += 4) {
+        uint4 v[4];
+        bool have[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          have[u] = (i0 + u < n_mine) && (static_cast<uint32_t>(tid) * 16u < chunk_len(i0 + u));
+          if (have[u])
+            v[u] = ptx::multimem_ld_reduce_bf16x8(static_cast<const char*>(p.mc_data) + base +
+                                                  chunk_off(i0 + u) + tid * 16);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (!have[u]) continue;
+          const long long off = base + chunk_off(i0 + u) + tid * 16;
+          if (OP == OP_RS) ptx::st_global_v4(static_cast<char*>(p.peer_data[s.rank]) + off, v[u]);
+          else ptx::multimem_st_v4(static_cast<char*>(p.mc_out) + off, v[u]);
+        }
+      }
+      continue;
+    }
+
+    // 2b. peer-to-peer path: bulk-copy the W partial chunks into shared memory, sum, store.
+    auto issue = [&](int i, long long at) {
+      const int slot = static_cast<int>(at % ns);
+      const uint32_t len = chunk_len(i);
+      const long long off = base + chunk_off(i);
+      ptx::mbar_expect_tx(bar(BAR_SLOT + slot), len * W);
+      for (int src = 0; src < W; ++src)
+        ptx::bulk_g2s(smem_base + slot * set_bytes + src * kReduceChunk,
+                      static_cast<const char*>(p.peer_data[src]) + off, len, bar(BAR_SLOT + slot));
+    };
+    if (tid == 0)
+      for (int i = 0; i < n_mine && i < ns; ++i) issue(i, pos + i);
+    for (int i = 0; i < n_mine; ++i, ++pos) {
+      const int slot = static_cast<int>(pos % ns);
+      const uint32_t parity = static_cast<uint32_t>((pos / ns) & 1);
+      bounded_wait<false>(wc, [&] { return ptx::mbar_try_wait(bar(BAR_SLOT + slot), parity); },
+                          ST_TIMEOUT_COPY, rb, i);
+      const uint32_t len = chunk_len(i);
+      if (static_cast<uint32_t>(tid) * 16u < len) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        const uint32_t src0 = smem_base + slot * set_bytes + tid * 16;
+        for (int src = 0; src < W; ++src)
+          accumulate_bf16x8(acc, ptx::ld_shared_v4(src0 + src * kReduceChunk));
+        uint4 v;
+        v.x = ptx::pack_bf16x2(acc[0], acc[1]);
+        v.y = ptx::pack_bf16x2(acc[2], acc[3]);
+        v.z = ptx::pack_bf16x2(acc[4], acc[5]);
+        v.w = ptx::pack_bf16x2(acc[6], acc[7]);
+        const long long off = base + chunk_off(i) + tid * 16;
+        if (OP == OP_RS) {
+          ptx::st_global_v4(static_cast<char*>(p.peer_data[s.rank]) + off, v);
+        } else {
+          for (int dst = 0; dst < W; ++dst)
+            ptx::st_global_v4(static_cast<char*>(p.peer_out[dst]) + off, v);
+        }
+      }
+      __syncthreads();  // every thread has read the slot
+      if (*wc.s_abort != 0u) return;
+      if (tid == 0 && i + ns < n_mine) issue(i + ns, pos + ns);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+// Kernel
+// ------------------------------------------------------------------------------------------
+template <int OP>
+__global__ void __launch_bounds__(kThreads, 1)
+fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
+                  const __grid_constant__ CUtensorMap tma_b,
+                  const __grid_constant__ OpParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const Sched& s = p.sched;
+  const int warp = threadIdx.x >> 5;
+  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int ring_bytes = p.stages * stage_bytes(s.block_n);
+  const uint32_t bar_base = smem_base + ring_bytes;
+  uint8_t* gen_base = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
+  volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(gen_base + ring_bytes + 8 * BAR_COUNT);
+  volatile uint32_t* s_abort = s_tmem + 1;
+  volatile uint32_t* s_epoch = s_tmem + 2;
+  const bool is_comm = static_cast<int>(blockIdx.x) < p.n_comm;
+
+  WaitCtx wc;
+  wc.status = p.status;
+  wc.s_abort = s_abort;
+  wc.limit_ns = p.wait_limit_ns;
+  wc.where = blockIdx.x << 8;
+
+  if (threadIdx.x == 0) {
+    *s_abort = 0u;
+    uint32_t e = p.epoch_arg;
+    if (p.sync != nullptr) {
+      if (OP == OP_AG) e = ptx::ld_relaxed_sys(p.sync + SW_EPOCH);
+      if (OP == OP_RS) e = ptx::ld_relaxed_sys(p.sync + SW_EPOCH) + 1u;
+    }
+    *s_epoch = e;
+    if (is_comm) {
+      for (int i = 0; i < 24; ++i) ptx::mbar_init(bar_base + 8u * (BAR_SLOT + i), 1);
+    } else {
+      for (int i = 0; i < kMaxStages; ++i) {
+        ptx::mbar_init(bar_base + 8u * (BAR_FULL + i), 1);
+        ptx::mbar_init(bar_base + 8u * (BAR_EMPTY + i), 1);
+      }
+      const bool publishes = (OP == OP_RS || OP == OP_AR) && s.world > 1;
+      for (int i = 0; i < 2; ++i) {
+        ptx::mbar_init(bar_base + 8u * (BAR_TFULL + i), 1);
+        ptx::mbar_init(bar_base + 8u * (BAR_TEMPTY + i), publishes ? 5 : 4);
+        ptx::mbar_init(bar_base + 8u * (BAR_STORED + i), 4);
+      }
+      ptx::tma_prefetch_desc(&tma_a);
+      ptx::tma_prefetch_desc(&tma_b);
+    }
+    ptx::fence_mbar_init();
+  }
+  if (!is_comm && warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(s_tmem)), 512);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t epoch = *s_epoch;
+
+  if (is_comm) {
+    if (OP == OP_AG) gather_cta(p, smem_base, bar_base, wc, epoch, ring_bytes);
+    if (OP == OP_RS || OP == OP_AR) reduce_cta<OP>(p, smem_base, bar_base, wc, epoch, ring_bytes);
+  } else {
+    compute_cta<OP>(&tma_a, &tma_b, p, smem_base, bar_base, s_tmem, wc, epoch);
+  }
+
+  // ---------------- teardown ----------------
+  if (*s_abort != 0u) {
+    // Leave time for copies this CTA still has in flight to land before its shared memory and
+    // tensor memory are released.
+    const uint64_t t0 = global_timer_ns();
+    while (global_timer_ns() - t0 < 50000ull) __nanosleep(1000);
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (!is_comm && warp == 1) {
+    __syncwarp();
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(*s_tmem, 512);
+  }
+  if (p.sync == nullptr || threadIdx.x != 0) return;
+
+  // ---------------- exit handshake (thread 0 of every CTA) ----------------
+  wc.where = (blockIdx.x << 8) | 15u;
+  if (is_comm && s.world > 1) {
+    // The exchange role of this rank is finished once all its exchange CTAs are.
+    ptx::fence_acq_rel_sys();
+    const uint32_t prev = atomicAdd(p.sync + SW_COMM_DONE, 1u);
+    if (prev == static_cast<uint32_t>(p.n_comm - 1)) {
+      ptx::fence_acq_rel_sys();
+      for (int r = 0; r < s.world; ++r) ptx::st_relaxed_sys(p.peer_sync[r] + SW_EXIT + s.rank, epoch);
+    }
+  }
+  __threadfence();
+  const uint32_t done = atomicAdd(p.sync + SW_GRID_DONE, 1u);
+  if (done == gridDim.x - 1) {
+    // Last CTA of this rank: the kernel may only end when every rank has finished reading this
+    // rank's buffers (and, for AllReduce, has written its share of this rank's output).
+    if (s.world > 1 && *s_abort == 0u) {
+      for (int r = 0; r < s.world; ++r) {
+        const uint32_t* f = p.sync + SW_EXIT + r;
+        if (!bounded_wait<true>(wc, [&] { return ptx::ld_acquire_sys(f) == epoch; },
+                                ST_TIMEOUT_EXIT, r, epoch))
+          break;
+      }
+    }
+    p.sync[SW_GRID_DONE] = 0u;
+    p.sync[SW_COMM_DONE] = 0u;
+    if (OP == OP_RS) p.sync[SW_EPOCH] = epoch;
+    __threadfence();
+  }
+}
+
+// Entry barrier of AllGather+GEMM (one warp): bump the device epoch, tell every peer, wait for
+// every peer.  After it every rank's previous launch has ended and every rank's shard is in place.
+// Stands in for prepare_epoch_barrier, src/ag_gemm_warp_specialized.cu:115-129.
+struct EntryParams {
+  uint32_t* sync;
+  uint32_t* peer_sync[kMaxWorld];
+  int rank, world;
+  uint64_t limit_ns;
+};
+__global__ void entry_barrier_kernel(const __grid_constant__ EntryParams e) {
+  __shared__ uint32_t s_abort;
+  __shared__ uint32_t s_epoch;
+  const int lane = threadIdx.x;
+  if (lane == 0) {
+    s_abort = 0u;
+    s_epoch = ptx::ld_relaxed_sys(e.sync + SW_EPOCH) + 1u;
+  }
+  __syncwarp();
+  const uint32_t epoch = s_epoch;
+  WaitCtx wc;
+  wc.status = e.sync + SW_STATUS;
+  wc.s_abort = &s_abort;
+  wc.limit_ns = e.limit_ns;
+  wc.where = 14u;
+  if (lane < e.world) {
+    ptx::fence_acq_rel_sys();
+    ptx::st_relaxed_sys(e.peer_sync[lane] + SW_ENTRY + e.rank, epoch);
+    const uint32_t* f = e.sync + SW_ENTRY + lane;
+    bounded_wait<true>(wc, [&] { return static_cast<int32_t>(ptx::ld_acquire_sys(f) - epoch) >= 0; },
+                       ST_TIMEOUT_ENTRY, lane, epoch);
+  }
+  __syncwarp();
+  if (lane == 0) {
+    e.sync[SW_EPOCH] = epoch;
+    __threadfence();
+  }
+}
+
+}  // namespace mkb

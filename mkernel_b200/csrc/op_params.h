@@ -1,0 +1,32 @@
+// Kernel parameter block shared by the host launcher and the persistent kernels.
+#pragma once
+#include <stdint.h>
+#include "sched.h"
+
+namespace mkb {
+
+struct OpParams {
+  Sched sched;
+  int K;
+  int k_blocks;          // ceil(K / 64)
+  int stages;            // operand ring depth
+  int b_mn_major;        // 0: B stored [N,K] (K contiguous); 1: B stored [K,N] (N contiguous)
+  int n_comm;            // CTAs [0, n_comm) run the exchange role, the rest run the GEMM
+  int use_nvls;          // exchange through NVSwitch multicast addresses when available
+  uint32_t epoch_arg;    // GEMM+AR: caller-provided epoch; other ops read SW_EPOCH
+  uint64_t wait_limit_ns;
+
+  void* C;               // GEMM output of this rank, bf16 row-major
+  long long ldc;         // elements
+  uint32_t* sync;        // this rank's synchronisation words (nullptr for the plain GEMM)
+  uint32_t* status;      // 4 status words: sync + SW_STATUS, or caller-provided, or nullptr
+  uint32_t* peer_sync[kMaxWorld];
+  // AG: every rank's gathered-A buffer ([W, M/W, K]); RS/AR: every rank's partial C ([M, N]).
+  void* peer_data[kMaxWorld];
+  // AR: every rank's C_final ([M, N]).  RS: unused (result overwrites the owner's slice of C).
+  void* peer_out[kMaxWorld];
+  void* mc_data;         // multicast alias of peer_data (or nullptr)
+  void* mc_out;          // multicast alias of peer_out (or nullptr)
+};
+
+}  // namespace mkb

@@ -1,0 +1,511 @@
+// Host side of the operators: argument validation, launch planning, TMA descriptor encoding and
+// the extern "C" entry points declared in include/mkernel_b200.h.
+//
+// Stands in for the reference's host entry points (semantics only):
+//   include/operators/ag_gemm/ag_gemm_warp_specialized.cuh:251-406 (globals, config table, launch)
+//   src/gemm_rs_blackwell.cu:642-732, include/operators/gemm_ar/gemm_ar_blackwell.cuh:205-246.
+// Differences by design: the world size is a run-time value (1..8); unsupported shapes return
+// MK_ERR_INVALID instead of silently launching nothing; no call exits the process.
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <mutex>
+
+#include "../../include/mkernel_b200.h"
+#include "fused_kernel.cuh"
+#include "host_util.h"
+
+namespace mkb {
+
+// ------------------------------------------------------------------------------------------
+// options
+// ------------------------------------------------------------------------------------------
+struct Options {
+  long long wait_limit_ms = 4000;
+  long long n_comm = 0;
+  long long block_n = 0;
+  long long group_rows = 0;
+  long long use_nvls = 0;
+};
+static Options g_opt;
+static std::mutex g_opt_mu;
+
+static long long* option_slot(const char* name) {
+  if (!name) return nullptr;
+  if (!strcmp(name, "wait_limit_ms")) return &g_opt.wait_limit_ms;
+  if (!strcmp(name, "n_comm")) return &g_opt.n_comm;
+  if (!strcmp(name, "block_n")) return &g_opt.block_n;
+  if (!strcmp(name, "group_rows")) return &g_opt.group_rows;
+  if (!strcmp(name, "use_nvls")) return &g_opt.use_nvls;
+  return nullptr;
+}
+
+// ------------------------------------------------------------------------------------------
+// planning (pure host arithmetic; also exported for tests)
+// ------------------------------------------------------------------------------------------
+struct Plan {
+  Sched sched;
+  int K, k_blocks, stages, n_comm, grid, smem;
+  int b_mn_major;
+};
+
+static int default_n_comm(int op, int world, int M, int N, int K, int num_sms) {
+  if (world <= 1 || op == OP_GEMM) return 0;
+  // Small, latency-bound problems cannot fill the machine with tiles even at the narrowest
+  // tile width: give every tile its own CTA and the rest (up to 32) to the exchange role.
+  const long long tiles64 = (long long)ceil_div(M, kBlockM) * ceil_div(N, 64);
+  if (tiles64 + 2 <= num_sms) {
+    int spare = num_sms - (int)tiles64;
+    return spare > 32 ? 32 : spare;
+  }
+  // Otherwise size the exchange role by the bytes this rank must move in per unit of GEMM time,
+  // assuming ~60 GB/s per exchange CTA (bulk-copy ring, ~180 KB in flight) and the GEMM running
+  // at ~1.2 PFLOP/s.
+  const double flops = 2.0 * M * (double)N * K;
+  double bytes_in;
+  if (op == OP_AG) bytes_in = (double)(world - 1) / world * M * (double)K * 2;
+  else bytes_in = (double)M * N * 2 * (op == OP_AR ? 1.5 : 1.0);  // W copies of a 1/W slice
+  const double t_gemm = flops / 1.2e15;
+  const double need = bytes_in / (t_gemm > 1e-9 ? t_gemm : 1e-9) / 60e9;
+  int n = (int)(need * 1.25 + 0.999);
+  if (n < 2) n = 2;
+  const int cap = num_sms / 5;
+  return n > cap ? cap : n;
+}
+
+static int make_plan(int op, int rank, int world, int M, int N, int K, int b_layout, int num_sms,
+                     Plan* out) {
+  if (op < OP_GEMM || op > OP_AR) return set_error(MK_ERR_INVALID, "unknown op %d", op);
+  if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world)
+    return set_error(MK_ERR_INVALID, "rank/world out of range: rank=%d world=%d", rank, world);
+  if (M < 1 || N < 1 || K < 1)
+    return set_error(MK_ERR_INVALID, "M, N, K must be positive (M=%d N=%d K=%d)", M, N, K);
+  if (N % 8 != 0 || K % 8 != 0)
+    return set_error(MK_ERR_INVALID, "N and K must be multiples of 8 (N=%d K=%d)", N, K);
+  if (op == OP_AG && M % world != 0)
+    return set_error(MK_ERR_INVALID, "AllGather+GEMM: M=%d not divisible by world=%d", M, world);
+  if (op == OP_RS && M % world != 0)
+    return set_error(MK_ERR_INVALID, "GEMM+ReduceScatter: M=%d not divisible by world=%d", M, world);
+  if (num_sms <= 0) num_sms = 148;
+
+  Options o;
+  {
+    std::lock_guard<std::mutex> g(g_opt_mu);
+    o = g_opt;
+  }
+  int n_comm = (int)o.n_comm > 0 && world > 1 && op != OP_GEMM
+                   ? (int)o.n_comm : default_n_comm(op, world, M, N, K, num_sms);
+  if (n_comm > num_sms - 1) n_comm = num_sms - 1;
+  const int n_comp_max = num_sms - n_comm;
+
+  const int quantum = b_layout == MK_B_KN ? 64 : 32;
+  int m_blocks = op == OP_AG ? world * ceil_div(M / world, kBlockM) : ceil_div(M, kBlockM);
+  int bn = (int)o.block_n;
+  if (bn <= 0) bn = choose_block_n(m_blocks, N, n_comp_max, quantum);
+  if (bn < 32 || bn > 256 || bn % quantum != 0)
+    return set_error(MK_ERR_INVALID, "block_n=%d must be a multiple of %d in [32,256]", bn, quantum);
+
+  int group = (int)o.group_rows;
+  if (group <= 0) group = 8;
+  Plan pl;
+  pl.sched = make_sched(op, rank, world, M, N, bn, group);
+  pl.K = K;
+  pl.k_blocks = ceil_div(K, kBlockK);
+  pl.stages = num_stages(bn);
+  pl.smem = smem_bytes(bn);
+  pl.b_mn_major = b_layout == MK_B_KN ? 1 : 0;
+  const long long tiles = (long long)pl.sched.P * pl.sched.Q;
+  int n_comp = tiles < n_comp_max ? (int)tiles : n_comp_max;
+  if (n_comp < 1) n_comp = 1;
+  pl.n_comm = n_comm;
+  pl.grid = n_comm + n_comp;
+  *out = pl;
+  return MK_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// TMA descriptors
+// ------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static int encode_2d_bf16(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer,
+                          uint64_t ld_elems, uint32_t box_inner, uint32_t box_outer) {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    int rc = driver_entry("cuTensorMapEncodeTiled", &p);
+    if (rc != MK_OK) return rc;
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0 || (ld_elems * 2) % 16 != 0)
+    return set_error(MK_ERR_INVALID, "operand base/stride must be 16-byte aligned");
+  const cuuint64_t dims[2] = {inner, outer};
+  const cuuint64_t strides[1] = {ld_elems * 2};
+  const cuuint32_t box[2] = {box_inner, box_outer};
+  const cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return set_error(MK_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return MK_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// launch
+// ------------------------------------------------------------------------------------------
+static int device_sm_count(int* out) {
+  static int cached[64];
+  int dev = 0;
+  MKB_CUDA(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && cached[dev] > 0) { *out = cached[dev]; return MK_OK; }
+  int n = 0;
+  MKB_CUDA(cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev));
+  int major = 0;
+  MKB_CUDA(cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev));
+  if (major != 10)
+    return set_error(MK_ERR_UNSUPPORTED, "device compute capability %d.x is not sm_100", major);
+  if (dev >= 0 && dev < 64) cached[dev] = n;
+  *out = n;
+  return MK_OK;
+}
+
+template <int OP>
+static int launch_kernel(const Plan& pl, const CUtensorMap& ta, const CUtensorMap& tb,
+                         const OpParams& p, cudaStream_t stream) {
+  auto kern = fused_gemm_kernel<OP>;
+  static bool attr_set[64];
+  int dev = 0;
+  MKB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !attr_set[dev]) {
+    MKB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
+    if (dev >= 0 && dev < 64) attr_set[dev] = true;
+  }
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3(pl.grid, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = pl.smem;
+  cfg.stream = stream;
+  cfg.attrs = nullptr;
+  cfg.numAttrs = 0;
+  MKB_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, tb, p));
+  return MK_OK;
+}
+
+struct OpArgs {
+  int op;
+  const void* A;       // GEMM A operand (AG: local gathered buffer)
+  long long a_rows;    // rows addressable through the A descriptor
+  const void* B;
+  void* C;
+  int M, N, K, b_layout;
+  int rank, world;
+  const mk_symm_view* sync;
+  const mk_symm_view* data;   // AG: A; RS/AR: C
+  const mk_symm_view* out;    // AR: C_final
+  uint32_t epoch;
+  uint32_t* status_only;      // plain GEMM: optional 4 status words
+};
+
+static int run_op(const OpArgs& a, cudaStream_t stream) {
+  int sms = 0;
+  int rc = device_sm_count(&sms);
+  if (rc != MK_OK) return rc;
+  Plan pl;
+  rc = make_plan(a.op, a.rank, a.world, a.M, a.N, a.K, a.b_layout, sms, &pl);
+  if (rc != MK_OK) return rc;
+  if (a.world > 1 && pl.n_comm < 1)
+    return set_error(MK_ERR_INVALID, "world > 1 needs at least one exchange CTA");
+
+  OpParams p;
+  memset(&p, 0, sizeof(p));
+  p.sched = pl.sched;
+  p.K = a.K;
+  p.k_blocks = pl.k_blocks;
+  p.stages = pl.stages;
+  p.b_mn_major = pl.b_mn_major;
+  p.n_comm = pl.n_comm;
+  p.epoch_arg = a.epoch;
+  {
+    std::lock_guard<std::mutex> g(g_opt_mu);
+    p.wait_limit_ns = (uint64_t)g_opt.wait_limit_ms * 1000000ull;
+    p.use_nvls = (int)g_opt.use_nvls;
+  }
+  p.C = a.C;
+  p.ldc = a.N;
+  if (a.sync) {
+    const long long need = sync_words_needed(pl.sched);
+    if ((long long)(a.sync->bytes / 4) < need)
+      return set_error(MK_ERR_INVALID, "synchronisation buffer holds %lld words, this shape needs %lld",
+                       (long long)(a.sync->bytes / 4), need);
+    p.sync = static_cast<uint32_t*>(a.sync->peer[a.rank]);
+    p.status = p.sync + SW_STATUS;
+    for (int r = 0; r < a.world; ++r) p.peer_sync[r] = static_cast<uint32_t*>(a.sync->peer[r]);
+  } else {
+    // The plain GEMM has no synchronisation buffer; it can still report a pipeline timeout
+    // through 4 caller-provided words laid out like SW_STATUS.
+    p.sync = nullptr;
+    p.status = a.status_only;
+  }
+  if (a.data) {
+    for (int r = 0; r < a.world; ++r) p.peer_data[r] = a.data->peer[r];
+    p.mc_data = a.data->mc;
+  }
+  if (a.out) {
+    for (int r = 0; r < a.world; ++r) p.peer_out[r] = a.out->peer[r];
+    p.mc_out = a.out->mc;
+  }
+  for (int r = 0; r < a.world; ++r) {
+    if ((a.sync && !p.peer_sync[r]) || (a.data && !p.peer_data[r]) || (a.out && !p.peer_out[r]))
+      return set_error(MK_ERR_INVALID, "symmetric view has no address for rank %d", r);
+  }
+
+  CUtensorMap ta, tb;
+  rc = encode_2d_bf16(&ta, a.A, (uint64_t)a.K, (uint64_t)a.a_rows, (uint64_t)a.K, kBlockK, kBlockM);
+  if (rc != MK_OK) return rc;
+  if (pl.b_mn_major)
+    rc = encode_2d_bf16(&tb, a.B, (uint64_t)a.N, (uint64_t)a.K, (uint64_t)a.N, 64, kBlockK);
+  else
+    rc = encode_2d_bf16(&tb, a.B, (uint64_t)a.K, (uint64_t)a.N, (uint64_t)a.K, kBlockK,
+                        (uint32_t)pl.sched.block_n);
+  if (rc != MK_OK) return rc;
+  if ((reinterpret_cast<uintptr_t>(a.C) & 15) != 0)
+    return set_error(MK_ERR_INVALID, "C must be 16-byte aligned");
+
+  switch (a.op) {
+    case OP_GEMM: return launch_kernel<OP_GEMM>(pl, ta, tb, p, stream);
+    case OP_AG: return launch_kernel<OP_AG>(pl, ta, tb, p, stream);
+    case OP_RS: return launch_kernel<OP_RS>(pl, ta, tb, p, stream);
+    case OP_AR: return launch_kernel<OP_AR>(pl, ta, tb, p, stream);
+  }
+  return set_error(MK_ERR_INVALID, "unknown op");
+}
+
+static int check_view(const mk_symm_view* v, const char* what, size_t min_bytes) {
+  if (!v) return set_error(MK_ERR_INVALID, "%s: null symmetric view", what);
+  if (v->world < 1 || v->world > kMaxWorld || v->rank < 0 || v->rank >= v->world)
+    return set_error(MK_ERR_INVALID, "%s: bad rank/world %d/%d", what, v->rank, v->world);
+  if (v->bytes < min_bytes)
+    return set_error(MK_ERR_INVALID, "%s: %zu bytes, need at least %zu", what, v->bytes, min_bytes);
+  if (!v->peer[v->rank]) return set_error(MK_ERR_INVALID, "%s: no local address", what);
+  return MK_OK;
+}
+
+}  // namespace mkb
+
+using namespace mkb;
+
+// ------------------------------------------------------------------------------------------
+// extern "C"
+// ------------------------------------------------------------------------------------------
+extern "C" {
+
+int mk_version(void) { return 100; }
+
+int mk_set_option(const char* name, long long value) {
+  std::lock_guard<std::mutex> g(g_opt_mu);
+  long long* s = option_slot(name);
+  if (!s) return set_error(MK_ERR_INVALID, "unknown option '%s'", name ? name : "(null)");
+  if (value < 0) return set_error(MK_ERR_INVALID, "option '%s' must be >= 0", name);
+  *s = value;
+  return MK_OK;
+}
+
+long long mk_get_option(const char* name) {
+  std::lock_guard<std::mutex> g(g_opt_mu);
+  long long* s = option_slot(name);
+  return s ? *s : -1;
+}
+
+int mk_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int b_layout,
+                 uint32_t* status4, void* stream) {
+  if (!A || !B || !C) return set_error(MK_ERR_INVALID, "mk_gemm_bf16: null operand");
+  OpArgs a;
+  memset(&a, 0, sizeof(a));
+  a.op = OP_GEMM; a.A = A; a.a_rows = M; a.B = B; a.C = C;
+  a.M = M; a.N = N; a.K = K; a.b_layout = b_layout; a.rank = 0; a.world = 1;
+  a.status_only = status4;
+  return run_op(a, static_cast<cudaStream_t>(stream));
+}
+
+int mk_ag_gemm_prepare(const mk_symm_view* ready, void* stream) {
+  int rc = check_view(ready, "ready", (size_t)MK_AG_READY_WORDS * 4);
+  if (rc != MK_OK) return rc;
+  EntryParams e;
+  memset(&e, 0, sizeof(e));
+  e.sync = static_cast<uint32_t*>(ready->peer[ready->rank]);
+  for (int r = 0; r < ready->world; ++r) {
+    if (!ready->peer[r]) return set_error(MK_ERR_INVALID, "ready: no address for rank %d", r);
+    e.peer_sync[r] = static_cast<uint32_t*>(ready->peer[r]);
+  }
+  e.rank = ready->rank;
+  e.world = ready->world;
+  {
+    std::lock_guard<std::mutex> g(g_opt_mu);
+    e.limit_ns = (uint64_t)g_opt.wait_limit_ms * 1000000ull;
+  }
+  entry_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(e);
+  MKB_CUDA(cudaGetLastError());
+  return MK_OK;
+}
+
+int mk_ag_gemm_launch(const mk_symm_view* A, const mk_symm_view* ready, const void* B, void* C,
+                      int M, int N, int K, void* stream) {
+  if (!B || !C) return set_error(MK_ERR_INVALID, "mk_ag_gemm_launch: null operand");
+  if (M < 1 || K < 1) return set_error(MK_ERR_INVALID, "mk_ag_gemm_launch: bad shape");
+  int rc = check_view(A, "A", (size_t)M * K * 2);
+  if (rc != MK_OK) return rc;
+  rc = check_view(ready, "ready", (size_t)MK_AG_READY_WORDS * 4);
+  if (rc != MK_OK) return rc;
+  if (A->world != ready->world || A->rank != ready->rank)
+    return set_error(MK_ERR_INVALID, "A and ready disagree on rank/world");
+  OpArgs a;
+  memset(&a, 0, sizeof(a));
+  a.op = OP_AG; a.A = A->peer[A->rank]; a.a_rows = M; a.B = B; a.C = C;
+  a.M = M; a.N = N; a.K = K; a.b_layout = MK_B_NK; a.rank = A->rank; a.world = A->world;
+  a.sync = ready; a.data = A;
+  return run_op(a, static_cast<cudaStream_t>(stream));
+}
+
+int mk_gemm_rs_prepare(const mk_symm_view* sync, void* stream) {
+  int rc = check_view(sync, "sync", (size_t)MK_RS_SYNC_WORDS * 4);
+  if (rc != MK_OK) return rc;
+  MKB_CUDA(cudaMemsetAsync(sync->peer[sync->rank], 0, sync->bytes, static_cast<cudaStream_t>(stream)));
+  return MK_OK;
+}
+
+int mk_gemm_rs_launch(const void* A, const void* B, const mk_symm_view* C,
+                      const mk_symm_view* sync, int M, int N, int K, void* stream) {
+  if (!A || !B) return set_error(MK_ERR_INVALID, "mk_gemm_rs_launch: null operand");
+  if (M < 1 || N < 1) return set_error(MK_ERR_INVALID, "mk_gemm_rs_launch: bad shape");
+  int rc = check_view(C, "C", (size_t)M * N * 2);
+  if (rc != MK_OK) return rc;
+  rc = check_view(sync, "sync", (size_t)SW_FLAGS * 4);
+  if (rc != MK_OK) return rc;
+  if (C->world != sync->world || C->rank != sync->rank)
+    return set_error(MK_ERR_INVALID, "C and sync disagree on rank/world");
+  OpArgs a;
+  memset(&a, 0, sizeof(a));
+  a.op = OP_RS; a.A = A; a.a_rows = M; a.B = B; a.C = C->peer[C->rank];
+  a.M = M; a.N = N; a.K = K; a.b_layout = MK_B_NK; a.rank = C->rank; a.world = C->world;
+  a.sync = sync; a.data = C;
+  return run_op(a, static_cast<cudaStream_t>(stream));
+}
+
+int mk_gemm_ar_launch(const void* A, const void* B, const mk_symm_view* C,
+                      const mk_symm_view* barrier, const mk_symm_view* C_final, int M, int N,
+                      int K, uint32_t epoch, int b_layout, void* stream) {
+  if (!A || !B) return set_error(MK_ERR_INVALID, "mk_gemm_ar_launch: null operand");
+  if (M < 1 || N < 1) return set_error(MK_ERR_INVALID, "mk_gemm_ar_launch: bad shape");
+  if (epoch == 0) return set_error(MK_ERR_INVALID, "mk_gemm_ar_launch: epoch must start at 1");
+  if (b_layout != MK_B_KN && b_layout != MK_B_NK)
+    return set_error(MK_ERR_INVALID, "mk_gemm_ar_launch: unknown B layout %d", b_layout);
+  int rc = check_view(C, "C", (size_t)M * N * 2);
+  if (rc != MK_OK) return rc;
+  rc = check_view(C_final, "C_final", (size_t)M * N * 2);
+  if (rc != MK_OK) return rc;
+  rc = check_view(barrier, "barrier", (size_t)SW_FLAGS * 4);
+  if (rc != MK_OK) return rc;
+  if (C->world != barrier->world || C->rank != barrier->rank || C_final->world != C->world ||
+      C_final->rank != C->rank)
+    return set_error(MK_ERR_INVALID, "C, C_final and barrier disagree on rank/world");
+  OpArgs a;
+  memset(&a, 0, sizeof(a));
+  a.op = OP_AR; a.A = A; a.a_rows = M; a.B = B;
+  a.M = M; a.N = N; a.K = K; a.b_layout = b_layout; a.rank = C->rank; a.world = C->world;
+  a.sync = barrier; a.data = C; a.out = C_final; a.epoch = epoch;
+  a.C = C->peer[C->rank];
+  rc = run_op(a, static_cast<cudaStream_t>(stream));
+  if (rc != MK_OK) return rc;
+  if (C->world == 1) {
+    // One GPU: the partial product is the result.
+    MKB_CUDA(cudaMemcpyAsync(C_final->peer[0], C->peer[0], (size_t)M * N * 2,
+                             cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)));
+  }
+  return MK_OK;
+}
+
+int mk_op_status(const mk_symm_view* sync, uint32_t out4[4]) {
+  int rc = check_view(sync, "sync", (size_t)SW_FLAGS * 4);
+  if (rc != MK_OK) return rc;
+  uint32_t w[4] = {0, 0, 0, 0};
+  MKB_CUDA(cudaMemcpy(w, static_cast<uint32_t*>(sync->peer[sync->rank]) + SW_STATUS, sizeof(w),
+                      cudaMemcpyDeviceToHost));
+  if (out4) memcpy(out4, w, sizeof(w));
+  if (w[0] != 0)
+    return set_error(MK_ERR_DEVICE_WAIT,
+                     "device wait expired: code=%u cta=%u role=%u detail=(%u,%u)", w[0], w[1] >> 8,
+                     w[1] & 255u, w[2], w[3]);
+  return MK_OK;
+}
+
+int mk_op_status_clear(const mk_symm_view* sync, void* stream) {
+  int rc = check_view(sync, "sync", (size_t)SW_FLAGS * 4);
+  if (rc != MK_OK) return rc;
+  MKB_CUDA(cudaMemsetAsync(static_cast<uint32_t*>(sync->peer[sync->rank]) + SW_STATUS, 0, 16,
+                           static_cast<cudaStream_t>(stream)));
+  return MK_OK;
+}
+
+int mk_plan_op(int op, int rank, int world, int M, int N, int K, int b_layout, int num_sms,
+               mk_plan* out) {
+  if (!out) return set_error(MK_ERR_INVALID, "mk_plan_op: null out");
+  Plan pl;
+  int rc = make_plan(op, rank, world, M, N, K, b_layout, num_sms, &pl);
+  if (rc != MK_OK) return rc;
+  out->block_n = pl.sched.block_n;
+  out->stages = pl.stages;
+  out->n_comm = pl.n_comm;
+  out->grid = pl.grid;
+  out->smem_bytes = pl.smem;
+  out->row_blocks = pl.sched.P;
+  out->col_blocks = pl.sched.Q;
+  out->k_blocks = pl.k_blocks;
+  out->part_rows = pl.sched.part_rows;
+  out->part_blocks = pl.sched.part_blocks;
+  out->interleave = pl.sched.interleave;
+  out->group_rows = pl.sched.group_rows;
+  out->sync_words = sync_words_needed(pl.sched);
+  return MK_OK;
+}
+
+int mk_sched_tiles(int op, int rank, int world, int M, int N, int block_n, int group_rows,
+                   int* row0, int* rows, int* col0, int* rowblock, int cap) {
+  if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world || block_n < 8 || M < 1 || N < 1)
+    return set_error(MK_ERR_INVALID, "mk_sched_tiles: bad arguments");
+  const Sched s = make_sched(op, rank, world, M, N, block_n, group_rows);
+  const int total = s.P * s.Q;
+  for (int t = 0; t < total && t < cap; ++t) {
+    int rb, q;
+    tile_to_coord(s, t, &rb, &q);
+    if (row0) row0[t] = rowblock_row0(s, rb);
+    if (rows) rows[t] = rowblock_rows(s, rb);
+    if (col0) col0[t] = q * block_n;
+    if (rowblock) rowblock[t] = rb;
+  }
+  return total;
+}
+
+int mk_sched_owner_items(int op, int world, int M, int N, int block_n, int owner, int* row0,
+                         int* row1, int cap) {
+  if (world < 1 || world > kMaxWorld || owner < 0 || owner >= world || M < 1 || N < 1)
+    return set_error(MK_ERR_INVALID, "mk_sched_owner_items: bad arguments");
+  const Sched s = make_sched(op, owner, world, M, N, block_n, 8);
+  const int n = owner_num_items(s, owner);
+  for (int k = 0; k < n && k < cap; ++k) {
+    int a, b;
+    owner_item_rows(s, owner, k, &a, &b);
+    if (row0) row0[k] = a;
+    if (row1) row1[k] = b;
+  }
+  return n;
+}
+
+}  // extern "C"

@@ -1,0 +1,201 @@
+// Tile scheduling and synchronisation-word layout shared by host and device code.
+//
+// All three fused operators run the same persistent bf16 GEMM over output tiles of
+// 128 rows x block_n columns.  What differs is (1) the order in which row-blocks are visited,
+// chosen so that the exchange step has work as early as possible, and (2) which flags a tile
+// waits for or raises.  Everything in this header is plain integer arithmetic so that the
+// same functions can be unit-tested on the host through the C ABI (mk_sched_* functions).
+//
+// Reference behaviour restated here (not its code): AllGather+GEMM visits the local shard first
+// and then shards at ring distance 1..W-1 (src/ag_gemm_warp_specialized.cu:243); the
+// reduce-scatter family interleaves the owners' slices so every owner's tiles become complete
+// progressively (include/operators/gemm_rs/gemm_rs.cuh:279-353).
+#pragma once
+#include <stdint.h>
+
+#if defined(__CUDACC__)
+#define MKB_HD __host__ __device__ __forceinline__
+#else
+#define MKB_HD inline
+#endif
+
+namespace mkb {
+
+constexpr int kMaxWorld = 8;
+constexpr int kBlockM = 128;
+constexpr int kBlockK = 64;
+constexpr int kThreads = 256;
+constexpr int kGatherSub = 8;          // AllGather: a 128-row block lands as 8 groups of 16 rows
+constexpr int kGatherChunk = 16384;    // bytes per bulk copy in the gather ring
+constexpr int kReduceChunk = 4096;     // bytes per peer per reduce step (256 threads x 16 B)
+constexpr int kMaxStages = 8;
+constexpr int kSmemBudget = 232448;    // 227 KiB opt-in limit per CTA on sm_100
+constexpr int kSmemBarrierBytes = 512;
+
+enum OpKind : int { OP_GEMM = 0, OP_AG = 1, OP_RS = 2, OP_AR = 3 };
+
+// Word offsets inside an operator's synchronisation buffer (uint32 words, caller-owned,
+// symmetric across ranks, zeroed once before first use).
+enum SyncWord : int {
+  SW_ENTRY = 0,       // [0,8): entry-barrier slot per source rank (AllGather prepare)
+  SW_EPOCH = 8,       // device-resident epoch (AG: bumped by prepare; RS: bumped at kernel exit)
+  SW_GRID_DONE = 9,   // CTAs that reached the end of the kernel (reset by the last one)
+  SW_COMM_DONE = 10,  // exchange CTAs that finished (reset by the last CTA)
+  SW_STATUS = 12,     // [12,16): {code, where, detail0, detail1}; 0 = healthy
+  SW_EXIT = 16,       // [16,24): exit slot per rank: "rank s finished its exchange role"
+  SW_FLAGS = 64,      // per-tile / per-row-group flags start here
+};
+
+// Status codes written to SW_STATUS (first failure wins).
+enum StatusCode : int {
+  ST_OK = 0,
+  ST_TIMEOUT_PIPE = 1,      // intra-CTA mbarrier wait expired
+  ST_TIMEOUT_GATHER = 2,    // AllGather: gathered-rows flag never arrived
+  ST_TIMEOUT_TILE = 3,      // reduce role: a peer's tile flag never arrived
+  ST_TIMEOUT_EXIT = 4,      // exit handshake: a peer never reported completion
+  ST_TIMEOUT_ENTRY = 5,     // entry barrier (prepare): a peer never arrived
+  ST_TIMEOUT_COPY = 6,      // exchange role: a bulk copy never completed
+};
+
+struct Sched {
+  int op;          // OpKind
+  int rank, world;
+  int M, N;        // rows / cols of this rank's GEMM output
+  int block_n;
+  int part_rows;   // AG: rows per gathered shard; RS/AR: rows per owner; GEMM: M
+  int part_blocks; // ceil(part_rows / 128)
+  int P;           // row-blocks: AG: world*part_blocks, else ceil(M/128)
+  int Q;           // column blocks: ceil(N / block_n)
+  int group_rows;  // raster group height in row-blocks
+  int interleave;  // RS/AR: 1 when part_rows % 128 == 0 (owner-interleaved order)
+};
+
+MKB_HD int ceil_div(int a, int b) { return (a + b - 1) / b; }
+
+MKB_HD Sched make_sched(int op, int rank, int world, int M, int N, int block_n, int group_rows) {
+  Sched s;
+  s.op = op; s.rank = rank; s.world = world; s.M = M; s.N = N; s.block_n = block_n;
+  if (op == OP_AG) s.part_rows = M / world;              // rows of one gathered shard
+  else if (op == OP_GEMM || world == 1) s.part_rows = M;
+  else s.part_rows = ceil_div(M, world);                 // rows reduced by one owner
+  if (s.part_rows < 1) s.part_rows = 1;
+  s.part_blocks = ceil_div(s.part_rows, kBlockM);
+  s.P = (op == OP_AG) ? world * s.part_blocks : ceil_div(M, kBlockM);
+  s.Q = ceil_div(N, block_n);
+  s.group_rows = group_rows < 1 ? 1 : group_rows;
+  s.interleave = ((op == OP_RS || op == OP_AR) && world > 1 && (s.part_rows % kBlockM) == 0 &&
+                  s.part_blocks * world == s.P) ? 1 : 0;
+  return s;
+}
+
+// i-th row-block in visiting order -> row-block id.
+//   AG: id = shard * part_blocks + j, shards visited local first then ring distance 1..W-1.
+//   RS/AR (interleaved): j-th block of owner (rank+1+d) % W, d fastest, so the own slice is last
+//   inside each round and every owner receives complete row-blocks round by round.
+MKB_HD int order_to_rowblock(const Sched& s, int i) {
+  if (s.op == OP_AG) {
+    const int d = i / s.part_blocks, j = i % s.part_blocks;
+    return ((s.rank + d) % s.world) * s.part_blocks + j;
+  }
+  if (s.interleave) {
+    const int j = i / s.world, d = i % s.world;
+    return ((s.rank + 1 + d) % s.world) * s.part_blocks + j;
+  }
+  return i;
+}
+
+// Linear tile index -> (row-block id, column block).  Tiles are rastered in groups of
+// group_rows row-blocks; inside a group the row-block index runs fastest so the CTAs working at
+// the same time share a few A row-blocks and a contiguous range of B column blocks in L2.
+MKB_HD void tile_to_coord(const Sched& s, int t, int* rowblock, int* q) {
+  const int per_group = s.group_rows * s.Q;
+  const int g = t / per_group, r = t % per_group;
+  const int first = g * s.group_rows;
+  const int rows_here = (s.P - first) < s.group_rows ? (s.P - first) : s.group_rows;
+  const int i = first + r % rows_here;
+  *q = r / rows_here;
+  *rowblock = order_to_rowblock(s, i);
+}
+
+MKB_HD int rowblock_row0(const Sched& s, int rb) {
+  if (s.op == OP_AG) return (rb / s.part_blocks) * s.part_rows + (rb % s.part_blocks) * kBlockM;
+  return rb * kBlockM;
+}
+MKB_HD int rowblock_rows(const Sched& s, int rb) {
+  if (s.op == OP_AG) {
+    const int left = s.part_rows - (rb % s.part_blocks) * kBlockM;
+    return left < kBlockM ? left : kBlockM;
+  }
+  const int left = s.M - rb * kBlockM;
+  return left < kBlockM ? left : kBlockM;
+}
+MKB_HD int rowblock_shard(const Sched& s, int rb) { return rb / s.part_blocks; }  // AG only
+
+// RS/AR: owners whose row range [o*part_rows, (o+1)*part_rows) intersects row-block rb.
+MKB_HD void rowblock_owners(const Sched& s, int rb, int* lo, int* hi) {
+  const int r0 = rb * kBlockM;
+  int r1 = r0 + kBlockM; if (r1 > s.M) r1 = s.M;
+  *lo = r0 / s.part_rows;
+  int h = (r1 - 1) / s.part_rows; if (h > s.world - 1) h = s.world - 1;
+  *hi = h;
+}
+
+// RS/AR reduce items of owner `o`: item k is the intersection of the owner's rows with
+// row-block (first_block + k).
+MKB_HD int owner_first_block(const Sched& s, int o) { return (o * s.part_rows) / kBlockM; }
+MKB_HD int owner_num_items(const Sched& s, int o) {
+  int r0 = o * s.part_rows, r1 = r0 + s.part_rows;
+  if (r1 > s.M) r1 = s.M;
+  if (r1 <= r0) return 0;
+  return (r1 - 1) / kBlockM - r0 / kBlockM + 1;
+}
+MKB_HD void owner_item_rows(const Sched& s, int o, int k, int* row0, int* row1) {
+  const int rb = owner_first_block(s, o) + k;
+  int a = rb * kBlockM, b = a + kBlockM;
+  const int r0 = o * s.part_rows;
+  int r1 = r0 + s.part_rows; if (r1 > s.M) r1 = s.M;
+  if (a < r0) a = r0;
+  if (b > r1) b = r1;
+  *row0 = a; *row1 = b;
+}
+
+// Flag indices (relative to SW_FLAGS).
+MKB_HD long long tile_flag_index(const Sched& s, int src, int rb, int q) {
+  return ((long long)src * s.P + rb) * s.Q + q;
+}
+MKB_HD long long gather_flag_index(int rb, int sub) { return (long long)rb * kGatherSub + sub; }
+MKB_HD long long sync_words_needed(const Sched& s) {
+  if (s.op == OP_AG) return SW_FLAGS + (long long)s.P * kGatherSub;
+  if (s.op == OP_RS || s.op == OP_AR) return SW_FLAGS + (long long)s.world * s.P * s.Q;
+  return SW_FLAGS;
+}
+
+// Shared-memory plan for one CTA.
+MKB_HD int stage_bytes(int block_n) { return kBlockM * kBlockK * 2 + block_n * kBlockK * 2; }
+MKB_HD int num_stages(int block_n) {
+  int n = (kSmemBudget - 1024 - kSmemBarrierBytes) / stage_bytes(block_n);
+  return n > kMaxStages ? kMaxStages : n;
+}
+MKB_HD int smem_bytes(int block_n) {
+  return 1024 + num_stages(block_n) * stage_bytes(block_n) + kSmemBarrierBytes;
+}
+
+// Column-block width: pick the multiple of `quantum` in [64, 256] that minimises the number of
+// full waves times the tile width (a proxy for time), preferring wider tiles on ties.
+// Widths below 128 make the MMA shared-memory bound, so they are considered only when 128-wide
+// tiles cannot give every compute CTA a tile (small, latency-bound problems).
+MKB_HD int choose_block_n(int M_blocks, int N, int n_compute_ctas, int quantum) {
+  int best = 256; long long best_cost = -1;
+  const int floor_bn = ((long long)M_blocks * ceil_div(N, 128) < n_compute_ctas) ? 64 : 128;
+  for (int bn = 256; bn >= floor_bn; bn -= quantum) {
+    const int q = ceil_div(N, bn);
+    const long long tiles = (long long)M_blocks * q;
+    const long long waves = (tiles + n_compute_ctas - 1) / n_compute_ctas;
+    // fixed per-tile overhead (epilogue hand-off, pipeline refill) ~ 24 columns' worth of MMA time
+    const long long cost = waves * (bn + 24);
+    if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
+  }
+  return best;
+}
+
+}  // namespace mkb

@@ -1,0 +1,140 @@
+"""Host-side operator functions with the reference's Python-callable signatures.
+
+Each function checks shapes the way the reference's pybind lambdas do and forwards raw pointers
+to the C ABI on the current torch CUDA stream.  References:
+  ag_gemm_warp_specialized_prepare/_launch  include/operators/ag_gemm/ag_gemm_warp_specialized_session.cuh:12-47
+  gemm_rs_blackwell_prepare/_launch         include/operators/gemm_rs/gemm_rs_blackwell_session.cuh:11-40
+  gemm_ar_intranode_blackwell               include/operators/gemm_ar/gemm_ar_blackwell.cuh:205-246
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+from .dist_buffer import DistBuffer
+
+ag_gemm_warp_specialized_ready_words = _lib.MK_AG_READY_WORDS
+gemm_rs_blackwell_sync_shape = (_lib.MK_RS_SYNC_WORDS,)
+gemm_ar_blackwell_barrier_shape = (2, 1024, 1024)
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _require(cond: bool, msg: str) -> None:
+    if not cond:
+        raise RuntimeError(msg)
+
+
+def _bf16_matrix(t: torch.Tensor, name: str) -> None:
+    _require(isinstance(t, torch.Tensor) and t.is_cuda, f"{name} must be a CUDA tensor")
+    _require(t.dtype == torch.bfloat16, f"{name} must be bfloat16")
+    _require(t.is_contiguous(), f"{name} must be contiguous")
+
+
+def gemm_bf16(A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, b_layout: int = _lib.MK_B_NK,
+              status: torch.Tensor | None = None) -> None:
+    """C[M,N] = A[M,K] @ B on one GPU; B is [N,K] (MK_B_NK) or [K,N] (MK_B_KN)."""
+    for t, n in ((A, "A"), (B, "B"), (C, "C")):
+        _bf16_matrix(t, n)
+    M, K = A.shape
+    N = B.shape[0] if b_layout == _lib.MK_B_NK else B.shape[1]
+    kb = B.shape[1] if b_layout == _lib.MK_B_NK else B.shape[0]
+    _require(kb == K, f"A and B disagree on K: {K} vs {kb}")
+    _require(tuple(C.shape) == (M, N), f"C must be [{M},{N}]")
+    with torch.cuda.device(A.device):
+        _lib.check(_lib.lib().mk_gemm_bf16(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K,
+                                           b_layout, status.data_ptr() if status is not None else None,
+                                           _stream()))
+
+
+def ag_gemm_warp_specialized_prepare(A_copy_ready: DistBuffer, M: int = 0, N: int = 0) -> None:
+    """All-rank entry barrier + epoch bump on the current stream (M, N kept for compatibility)."""
+    _require(isinstance(A_copy_ready, DistBuffer), "A_copy_ready must be a DistBuffer")
+    with torch.cuda.device(A_copy_ready.local_rank_):
+        _lib.check(_lib.lib().mk_ag_gemm_prepare(A_copy_ready.view_ref(), _stream()))
+
+
+def ag_gemm_warp_specialized_launch(A: DistBuffer, A_copy_ready: DistBuffer, B: torch.Tensor,
+                                    C: torch.Tensor) -> None:
+    """C[d] = A_shard[d] @ B^T for every shard d.  A: DistBuffer [W, M/W, K]; B: [N, K];
+    C: [W, M/W, N]."""
+    _require(isinstance(A, DistBuffer) and isinstance(A_copy_ready, DistBuffer),
+             "A and A_copy_ready must be DistBuffers")
+    _require(A.dtype == torch.bfloat16 and len(A.shape) == 3, "A must be bf16 [W, M/W, K]")
+    _bf16_matrix(B, "B")
+    _require(C.dtype == torch.bfloat16 and C.is_cuda and C.is_contiguous() and C.dim() == 3,
+             "C must be a contiguous bf16 CUDA tensor [W, M/W, N]")
+    W, Ms, K = A.shape
+    _require(W == A.local_world_size_, "A.shape[0] must equal the local world size")
+    N = B.size(0)
+    _require(B.size(1) == K, f"B must be [N, K] with K={K}")
+    _require(tuple(C.shape) == (W, Ms, N), f"C must be [{W},{Ms},{N}]")
+    with torch.cuda.device(A.local_rank_):
+        _lib.check(_lib.lib().mk_ag_gemm_launch(A.view_ref(), A_copy_ready.view_ref(),
+                                                B.data_ptr(), C.data_ptr(), W * Ms, N, K,
+                                                _stream()))
+
+
+def gemm_rs_blackwell_prepare(A, B, C: DistBuffer, sync: DistBuffer) -> None:
+    """Zero the synchronisation words once; the caller then synchronises and barriers."""
+    _require(isinstance(sync, DistBuffer), "sync must be a DistBuffer")
+    with torch.cuda.device(sync.local_rank_):
+        _lib.check(_lib.lib().mk_gemm_rs_prepare(sync.view_ref(), _stream()))
+
+
+def gemm_rs_blackwell_launch(A: torch.Tensor, B: torch.Tensor, C: DistBuffer,
+                             sync: DistBuffer) -> None:
+    """Partial C = A @ B^T, then rows [rank*M/W, (rank+1)*M/W) of C.data_ hold the sum over ranks."""
+    _bf16_matrix(A, "A")
+    _bf16_matrix(B, "B")
+    _require(isinstance(C, DistBuffer) and isinstance(sync, DistBuffer),
+             "C and sync must be DistBuffers")
+    M, K = A.shape
+    N = B.size(0)
+    _require(B.size(1) == K, f"B must be [N, K] with K={K}")
+    _require(C.dtype == torch.bfloat16 and tuple(C.shape) == (M, N), f"C must be bf16 [{M},{N}]")
+    with torch.cuda.device(C.local_rank_):
+        _lib.check(_lib.lib().mk_gemm_rs_launch(A.data_ptr(), B.data_ptr(), C.view_ref(),
+                                                sync.view_ref(), M, N, K, _stream()))
+
+
+def gemm_ar_intranode_blackwell(A: torch.Tensor, B: torch.Tensor, C: DistBuffer,
+                                barrier: DistBuffer, C_final: DistBuffer, epoch: int,
+                                b_layout: int = _lib.MK_B_KN) -> None:
+    """C_final = sum over ranks of A_r @ B_r on every rank; C receives this rank's partial."""
+    _bf16_matrix(A, "A")
+    _bf16_matrix(B, "B")
+    for d, n in ((C, "C"), (barrier, "barrier"), (C_final, "C_final")):
+        _require(isinstance(d, DistBuffer), f"{n} must be a DistBuffer")
+    M, K = A.shape
+    if b_layout == _lib.MK_B_KN:
+        _require(B.size(0) == K, f"B must be [K, N] with K={K}")
+        N = B.size(1)
+    else:
+        _require(B.size(1) == K, f"B must be [N, K] with K={K}")
+        N = B.size(0)
+    for d, n in ((C, "C"), (C_final, "C_final")):
+        _require(d.dtype == torch.bfloat16 and tuple(d.shape) == (M, N), f"{n} must be bf16 [{M},{N}]")
+    _require(int(epoch) >= 1, "epoch starts at 1 and must increase by one per call")
+    with torch.cuda.device(C.local_rank_):
+        _lib.check(_lib.lib().mk_gemm_ar_launch(A.data_ptr(), B.data_ptr(), C.view_ref(),
+                                                barrier.view_ref(), C_final.view_ref(), M, N, K,
+                                                int(epoch), b_layout, _stream()))
+
+
+def op_status(sync: DistBuffer) -> tuple[int, int, int, int]:
+    """Status words of an operator's synchronisation buffer; raises MkError if a device wait
+    expired.  Synchronises the device."""
+    out = (ctypes.c_uint32 * 4)()
+    with torch.cuda.device(sync.local_rank_):
+        _lib.check(_lib.lib().mk_op_status(sync.view_ref(), out))
+    return tuple(int(x) for x in out)
+
+
+def op_status_clear(sync: DistBuffer) -> None:
+    with torch.cuda.device(sync.local_rank_):
+        _lib.check(_lib.lib().mk_op_status_clear(sync.view_ref(), _stream()))

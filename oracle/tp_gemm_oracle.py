@@ -1,0 +1,147 @@
+"""CPU oracle for the tensor-parallel GEMM + collective operators.  TEST INFRASTRUCTURE ONLY:
+nothing in the product package imports this file; it is the checker for tests/, for
+__graft_entry__.smoke() and for bench.py's CPU baseline.
+
+It restates, in plain torch-on-CPU / numpy, the computation the reference's own check mode
+treats as ground truth (the reference has no golden files; its checks compare the fused kernels
+with torch.matmul + torch.distributed collectives on seeded inputs):
+
+  AllGather+GEMM    A_full = cat_r(A_r); C = A_full @ B           bench/ag_gemm_bench.py:554-568
+  GEMM+ReduceScatter out_r = (sum_s A_s @ B_s^T)[r*M/W:(r+1)*M/W] bench/gemm_rs_bench.py:408-410, 433-435
+  GEMM+AllReduce    C = sum_s A_s @ B_s on every rank             bench/gemm_ar_blackwell_bench.py:423-438
+  acceptance        three-tier check_close                        bench/common.py:312-367
+
+Arithmetic contract: operands are bf16 values; products and sums are taken in fp32 (or fp64 with
+``exact=True``) over the bf16-rounded operands; results are compared before any rounding of the
+oracle's output, so the tolerance covers exactly one bf16 rounding plus accumulation order.
+
+Pinning: the reference ships no golden vectors for this path.  This oracle is pinned by
+(a) tests/golden/check_close_cases.json, produced by running the reference's own
+bench/common.py:check_close (imported from the reference tree, single-process gloo group) on
+seeded cases -- see tests/golden/make_golden.py -- and (b) the reference torch path itself
+(torch.matmul + gloo collectives) run as processes in tests/test_oracle_gloo.py.  The numeric
+outputs of the three operators have no reference-held fixtures: parity of those is "unpinned"
+beyond (b).
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Sequence
+
+import numpy as np
+import torch
+
+# ---------------------------------------------------------------------------------------------
+# bf16 helpers (numpy has no bf16; round-to-nearest-even on the top 16 bits of fp32)
+# ---------------------------------------------------------------------------------------------
+
+
+def bf16_round_np(x: np.ndarray) -> np.ndarray:
+    """Round fp32 values to the nearest bf16 (ties to even), returned as fp32."""
+    u = np.asarray(x, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    rounded = ((u + 0x7FFF + ((u >> 16) & 1)) >> 16) << 16
+    return rounded.astype(np.uint32).view(np.float32)
+
+
+def synth_inputs(kind: str, rank: int, world: int, M: int, N: int, K: int, seed: int,
+                 sigma_b: float | None = None):
+    """Seeded synthetic operands with the distributions BASELINE's configs state:
+    A ~ N(0,1), B ~ N(0, sigma_b^2) with sigma_b = 1/sqrt(K_total) unless given; seed + rank.
+
+    kind "ag": A_r [M/W, K], B [K, N] (logical).   kind "rs"/"ar": A_r [M, K], B_r [K, N]
+    (K is the per-rank contraction length; sigma uses K * world).
+    Returns bf16 tensors on CPU.
+    """
+    g = torch.Generator().manual_seed(seed + rank)
+    if kind == "ag":
+        rows, k_total = M // world, K
+    else:
+        rows, k_total = M, K * world
+    if sigma_b is None:
+        sigma_b = 1.0 / math.sqrt(k_total)
+    A = torch.randn((rows, K), generator=g, dtype=torch.float32)
+    B = torch.randn((K, N), generator=g, dtype=torch.float32) * sigma_b
+    return A.to(torch.bfloat16), B.to(torch.bfloat16)
+
+
+def _mm(a: torch.Tensor, b: torch.Tensor, exact: bool) -> torch.Tensor:
+    dt = torch.float64 if exact else torch.float32
+    return a.to(dt) @ b.to(dt)
+
+
+# ---------------------------------------------------------------------------------------------
+# the three operators
+# ---------------------------------------------------------------------------------------------
+
+
+def ag_gemm_ref(A_shards: Sequence[torch.Tensor], B_kn: torch.Tensor, exact: bool = False):
+    """AllGather+GEMM.  A_shards[r]: [M/W, K] bf16; B_kn: [K, N] bf16 (this rank's columns).
+    Returns (A_full [M, K] bf16 -- must match the gathered buffer bit for bit,
+             C [M, N] fp32/fp64)."""
+    A_full = torch.cat(list(A_shards), dim=0)
+    return A_full, _mm(A_full, B_kn, exact)
+
+
+def gemm_rs_ref(A_list: Sequence[torch.Tensor], B_kn_list: Sequence[torch.Tensor],
+                exact: bool = False) -> List[torch.Tensor]:
+    """GEMM+ReduceScatter.  A_list[s]: [M, K_s]; B_kn_list[s]: [K_s, N].  Returns out[r] =
+    rows [r*M/W, (r+1)*M/W) of sum_s A_s @ B_s."""
+    W = len(A_list)
+    total = None
+    for a, b in zip(A_list, B_kn_list):
+        p = _mm(a, b, exact)
+        total = p if total is None else total + p
+    M = total.shape[0]
+    assert M % W == 0
+    return [total[r * (M // W):(r + 1) * (M // W)] for r in range(W)]
+
+
+def gemm_ar_ref(A_list: Sequence[torch.Tensor], B_kn_list: Sequence[torch.Tensor],
+                exact: bool = False):
+    """GEMM+AllReduce.  Returns (C = sum_s A_s @ B_s, [partial_s])."""
+    partials = [_mm(a, b, exact) for a, b in zip(A_list, B_kn_list)]
+    total = partials[0].clone()
+    for p in partials[1:]:
+        total = total + p
+    return total, partials
+
+
+# ---------------------------------------------------------------------------------------------
+# acceptance
+# ---------------------------------------------------------------------------------------------
+
+
+def check_close_stats(observed: torch.Tensor, expected: torch.Tensor, atol: float = 0.35,
+                      rtol: float = 0.08, mean_rtol: float = 0.01) -> dict:
+    """The reference's three-tier acceptance (bench/common.py:312-367) on one rank:
+    pass if max_abs <= atol, or max_rel <= rtol (denominator clamped at 1e-6), or
+    mean_abs <= mean_rtol * mean|expected|."""
+    o = observed.detach().float()
+    e = expected.detach().float()
+    diff = (o - e).abs()
+    n = diff.numel()
+    max_abs = float(diff.max()) if n else 0.0
+    mean_abs = float(diff.mean()) if n else 0.0
+    ref_mean = float(e.abs().mean()) if n else 0.0
+    max_rel = float((diff / e.abs().clamp_min(1e-6)).max()) if n else 0.0
+    bulk_clean = mean_abs <= mean_rtol * max(ref_mean, 1e-6)
+    ok = (max_abs <= atol) or (max_rel <= rtol) or bulk_clean
+    return {"ok": bool(ok), "max_abs": max_abs, "max_rel": max_rel, "mean_abs": mean_abs,
+            "ref_mean": ref_mean, "bulk_clean": bool(bulk_clean)}
+
+
+def rel_error(observed: torch.Tensor, expected: torch.Tensor) -> float:
+    """The build's own acceptance metric: max over elements of
+    |observed - expected| / max(|expected|, rms(expected)).  A plain elementwise relative error
+    is unbounded where the reference crosses zero, so the denominator is floored at the RMS of
+    the reference.  The bound for bf16 outputs of fp32-accumulated products is 1e-2."""
+    o = observed.detach().double()
+    e = expected.detach().double()
+    if e.numel() == 0:
+        return 0.0
+    rms = float(e.pow(2).mean().sqrt())
+    denom = e.abs().clamp_min(max(rms, 1e-30))
+    return float(((o - e).abs() / denom).max())
+
+
+REL_TOL = 1e-2
