@@ -1,0 +1,78 @@
+"""The C-ABI library loads on a machine without a GPU and exports every symbol the public
+header declares; argument errors come back as codes + messages, never as a process exit."""
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+from mkernel_b200 import _lib
+
+HEADER = Path(__file__).resolve().parent.parent / "include" / "mkernel_b200.h"
+
+
+def declared_symbols():
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return sorted(set(re.findall(r"\b(mk_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported():
+    lib = _lib.lib()
+    names = declared_symbols()
+    assert len(names) >= 20
+    for name in names:
+        assert hasattr(lib, name), f"{name} declared in mkernel_b200.h but not exported"
+
+
+def test_binding_covers_header():
+    assert set(declared_symbols()) == set(_lib._SIGNATURES)
+
+
+def test_version():
+    assert _lib.lib().mk_version() >= 100
+
+
+def test_invalid_arguments_return_codes():
+    lib = _lib.lib()
+    assert lib.mk_gemm_bf16(None, None, None, 128, 128, 64, 0, None, None) == -1
+    assert "null operand" in _lib.last_error()
+    assert lib.mk_set_option(b"no_such_option", 1) == -1
+    out = ctypes.c_void_p()
+    assert lib.mk_comm_create(b"k", 9, 8, 0, ctypes.byref(out)) == -1
+    assert lib.mk_comm_create(b"k", 0, 9, 0, ctypes.byref(out)) == -1
+    with pytest.raises(_lib.MkError):
+        _lib.plan_op(_lib.OP_AG, 0, 8, 8190, 3584, 8192)       # M not divisible by world
+    with pytest.raises(_lib.MkError):
+        _lib.plan_op(_lib.OP_RS, 0, 8, 8192, 8191, 3584)       # N not a multiple of 8
+
+
+def test_options_roundtrip():
+    assert _lib.get_option("wait_limit_ms") == 4000
+    _lib.set_option("wait_limit_ms", 1000)
+    assert _lib.get_option("wait_limit_ms") == 1000
+    _lib.set_option("wait_limit_ms", 4000)
+    with pytest.raises(_lib.MkError):
+        _lib.set_option("block_n", -5)
+
+
+def test_view_validation_without_gpu():
+    lib = _lib.lib()
+    v = _lib.SymmView()
+    v.rank, v.world, v.bytes = 0, 1, 16
+    assert lib.mk_ag_gemm_prepare(ctypes.byref(v), None) == -1      # too small, no address
+    v.world = 99
+    assert lib.mk_gemm_rs_prepare(ctypes.byref(v), None) == -1
+
+
+def test_loader_names():
+    import mkernel_b200
+    mod = mkernel_b200.load("ag_gemm_warp_specialized")
+    assert mod.__name__ == "mkernel_release_ag_gemm_warp_specialized"
+    assert mod.ag_gemm_warp_specialized_ready_words == _lib.MK_AG_READY_WORDS
+    assert callable(mod.ag_gemm_warp_specialized_launch) and hasattr(mod, "DistBuffer")
+    mod = mkernel_b200.load("gemm_rs_blackwell")
+    assert tuple(mod.gemm_rs_blackwell_sync_shape) == (524288,)
+    mod = mkernel_b200.load("gemm_ar_blackwell")
+    assert callable(mod.gemm_ar_intranode_blackwell)
+    with pytest.raises(RuntimeError):
+        mkernel_b200.load("ring_attention")

@@ -1,0 +1,105 @@
+"""Host-side checks of the tile scheduler and launch planner (the same functions the kernels
+call on the device, reached through the C ABI)."""
+import pytest
+
+from mkernel_b200 import _lib
+from mkernel_b200._lib import OP_AG, OP_AR, OP_GEMM, OP_RS
+
+CONFIGS = [
+    # op, world, M, N, K, layout   (BASELINE configs 2, 3, 4 and sweep corners)
+    (OP_AG, 8, 8192, 3584, 8192, 0),
+    (OP_RS, 8, 8192, 8192, 3584, 0),
+    (OP_AR, 8, 128, 8192, 1024, 1),
+    (OP_AG, 1, 32768, 28672, 8192, 0),
+    (OP_AG, 2, 2048, 14336, 8192, 0),
+    (OP_RS, 4, 32768, 8192, 7168, 0),
+    (OP_RS, 2, 2048, 8192, 14336, 0),
+    (OP_AR, 8, 8192, 8192, 1024, 1),
+    (OP_GEMM, 1, 200, 264, 136, 0),
+    (OP_AR, 8, 100, 264, 72, 0),
+    (OP_AG, 8, 8 * 200, 264, 136, 0),
+]
+
+
+@pytest.mark.parametrize("op,world,M,N,K,layout", CONFIGS)
+def test_plan_is_launchable(op, world, M, N, K, layout):
+    for rank in range(world):
+        p = _lib.plan_op(op, rank, world, M, N, K, layout, 148)
+        assert p.smem_bytes <= 232448
+        assert 1 <= p.grid <= 148
+        assert p.stages >= 2 and p.block_n % (64 if layout else 32) == 0
+        assert (p.n_comm >= 1) == (world > 1 and op != OP_GEMM)
+        cap = {OP_AG: _lib.MK_AG_READY_WORDS, OP_RS: _lib.MK_RS_SYNC_WORDS,
+               OP_AR: _lib.MK_AR_BARRIER_WORDS}.get(op)
+        if cap:
+            assert p.sync_words <= cap
+
+
+@pytest.mark.parametrize("op,world,M,N,K,layout", CONFIGS)
+def test_every_output_element_is_covered_once(op, world, M, N, K, layout):
+    p = _lib.plan_op(op, 0, world, M, N, K, layout, 148)
+    for rank in {0, world - 1}:
+        tiles = _lib.sched_tiles(op, rank, world, M, N, p.block_n, p.group_rows)
+        assert len(tiles) == p.row_blocks * p.col_blocks
+        seen = set()
+        area = 0
+        for row0, rows, col0, rb in tiles:
+            assert 1 <= rows <= 128 and row0 % 1 == 0
+            assert (row0, col0) not in seen
+            seen.add((row0, col0))
+            area += rows * min(p.block_n, N - col0)
+        assert area == M * N
+
+
+def test_allgather_visits_local_shard_first_then_ring():
+    world, M, N = 8, 8192, 3584
+    for rank in (0, 3, 7):
+        tiles = _lib.sched_tiles(OP_AG, rank, world, M, N, 256, 8)
+        shards = [row0 // (M // world) for row0, _, _, _ in tiles]
+        order = []
+        for s in shards:
+            if not order or order[-1] != s:
+                order.append(s)
+        assert order == [(rank + d) % world for d in range(world)]
+
+
+def test_reduce_scatter_interleaves_owners_own_slice_last():
+    world, M, N = 8, 8192, 8192
+    rank = 2
+    tiles = _lib.sched_tiles(OP_RS, rank, world, M, N, 256, 8)
+    # group_rows = 8 = world: each raster group holds one row-block of every owner
+    per_group = 8 * (N // 256)
+    first = tiles[:per_group]
+    owners = sorted({row0 // (M // world) for row0, _, _, _ in first})
+    assert owners == list(range(world))
+    # within a group the row-block index runs fastest: the 8th tile belongs to this rank
+    assert [row0 // (M // world) for row0, _, _, _ in first[:8]] == \
+        [(rank + 1 + d) % world for d in range(world)]
+    # every owner's j-th row-block is visited in round j
+    for idx, (row0, _, _, _) in enumerate(tiles):
+        assert (row0 % (M // world)) // 128 == idx // per_group
+
+
+@pytest.mark.parametrize("op,world,M,N", [(OP_RS, 8, 8192, 8192), (OP_AR, 8, 128, 8192),
+                                          (OP_AR, 8, 100, 264), (OP_AR, 4, 1000, 512),
+                                          (OP_RS, 2, 384, 256)])
+def test_owner_items_partition_the_rows(op, world, M, N):
+    covered = []
+    for owner in range(world):
+        items = _lib.sched_owner_items(op, world, M, N, 128, owner)
+        for a, b in items:
+            assert 0 <= a < b <= M and b - a <= 128
+            assert a // 128 == (b - 1) // 128          # an item never straddles a row-block
+            covered.extend(range(a, b))
+    assert covered == list(range(M))
+
+
+def test_block_width_avoids_wave_quantisation():
+    # 8192 x 3584 on 148 CTAs: 256-wide tiles need 7 waves for 6.05 waves of work
+    p = _lib.plan_op(OP_GEMM, 0, 1, 8192, 3584, 8192, 0, 148)
+    tiles = p.row_blocks * p.col_blocks
+    waves = -(-tiles // p.grid)
+    assert tiles / (waves * p.grid) > 0.95
+    # decode-shaped all-reduce: every tile gets its own CTA
+    p = _lib.plan_op(OP_AR, 0, 8, 128, 8192, 1024, 1, 148)
+    assert p.row_blocks * p.col_blocks <= p.grid - p.n_comm
