@@ -1,0 +1,190 @@
+"""One rank of a multi-GPU parity run (spawned by test_multi_gpu.py, also usable by hand:
+``python -m torch.distributed.run --nproc-per-node 2 tests/multi_gpu_worker.py``).
+
+Every rank regenerates all ranks' seeded inputs on the CPU, computes the oracle result for the
+rows it checks, runs the fused operator through the reference-shaped API and returns the error
+figures.  Host coordination uses a gloo group; the operators use only their own transport.
+"""
+from __future__ import annotations
+
+import json
+import os
+import sys
+import traceback
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+
+import mkernel_b200  # noqa: E402
+from mkernel_b200 import _lib  # noqa: E402
+from oracle import tp_gemm_oracle as orc  # noqa: E402
+
+
+def _sample_rows(n_rows: int, max_rows: int, seed: int) -> torch.Tensor:
+    if n_rows <= max_rows:
+        return torch.arange(n_rows)
+    g = torch.Generator().manual_seed(seed)
+    return torch.randperm(n_rows, generator=g)[:max_rows].sort().values
+
+
+def sync_all():
+    torch.cuda.synchronize()
+    dist.barrier()
+
+
+def case_ag(rank, world, M, N, K, seed, iters, max_rows, multicast=False):
+    mod = mkernel_b200.load("ag_gemm_warp_specialized")
+    dev = torch.device("cuda", rank)
+    Ms = M // world
+    shards = [orc.synth_inputs("ag", r, world, M, N, K, seed=seed)[0] for r in range(world)]
+    b_kn = orc.synth_inputs("ag", rank, world, M, N, K, seed=seed)[1]
+    A = mod.DistBuffer((world, Ms, K), dtype=torch.bfloat16, local_rank=rank,
+                       local_world_size=world, multicast=multicast)
+    A.data_.zero_()
+    A.data_[rank].copy_(shards[rank])
+    ready = mod.DistBuffer((mod.ag_gemm_warp_specialized_ready_words,), dtype=torch.int32,
+                           local_rank=rank, local_world_size=world, multicast=multicast)
+    ready.data_.zero_()
+    B = b_kn.t().contiguous().to(dev)
+    C = torch.zeros((world, Ms, N), device=dev, dtype=torch.bfloat16)
+    sync_all()
+    rows = _sample_rows(M, max_rows, seed)
+    a_full = torch.cat(shards, 0)
+    ref = a_full[rows].float() @ b_kn.float()
+    res = dict(op="ag", M=M, N=N, K=K, rel=[], gathered_exact=[], status=[])
+    for it in range(iters):
+        C.zero_()
+        if it > 0:  # poison the remote slabs so a stale gather would be noticed
+            for r in range(world):
+                if r != rank:
+                    A.data_[r].zero_()
+            sync_all()
+        mod.ag_gemm_warp_specialized_prepare(ready, M, N)
+        mod.ag_gemm_warp_specialized_launch(A, ready, B, C)
+        torch.cuda.synchronize()
+        res["status"].append(list(mod.op_status(ready)) if True else None)
+        res["gathered_exact"].append(bool(torch.equal(A.data_.view(M, K).cpu(), a_full)))
+        res["rel"].append(orc.rel_error(C.view(M, N)[rows.to(dev)].cpu(), ref))
+        dist.barrier()
+    sync_all()
+    return res
+
+
+def case_rs(rank, world, M, N, K, seed, iters, max_rows, multicast=False):
+    mod = mkernel_b200.load("gemm_rs_blackwell")
+    dev = torch.device("cuda", rank)
+    Ms = M // world
+    rows = _sample_rows(Ms, max_rows, seed)
+    ref = None
+    mine = None
+    for r in range(world):
+        a, b = orc.synth_inputs("rs", r, world, M, N, K, seed=seed)
+        p = a[rank * Ms + rows].float() @ b.float()
+        ref = p if ref is None else ref + p
+        if r == rank:
+            mine = (a, b)
+    A = mine[0].to(dev)
+    B = mine[1].t().contiguous().to(dev)
+    C = mod.DistBuffer((M, N), dtype=torch.bfloat16, local_rank=rank, local_world_size=world,
+                       multicast=multicast)
+    sync = mod.DistBuffer(mod.gemm_rs_blackwell_sync_shape, dtype=torch.int32, local_rank=rank,
+                          local_world_size=world, multicast=False)
+    mod.gemm_rs_blackwell_prepare(A, B, C, sync)
+    sync_all()
+    res = dict(op="rs", M=M, N=N, K=K, rel=[], status=[])
+    sign = 1.0
+    for it in range(iters):
+        if it > 0:      # back-to-back launches without host barriers; A negated in between
+            A.neg_()
+            sign = -sign
+        mod.gemm_rs_blackwell_launch(A, B, C, sync)
+        torch.cuda.synchronize()
+        out = C.data_.narrow(0, rank * Ms, Ms)
+        res["rel"].append(orc.rel_error(out[rows.to(dev)].cpu(), sign * ref))
+        res["status"].append(list(mod.op_status(sync)))
+        dist.barrier()   # the reduced slice is read above before any rank launches again
+    sync_all()
+    return res
+
+
+def case_ar(rank, world, M, N, K, seed, iters, max_rows, layout=_lib.MK_B_KN, multicast=False):
+    mod = mkernel_b200.load("gemm_ar_blackwell")
+    dev = torch.device("cuda", rank)
+    rows = _sample_rows(M, max_rows, seed)
+    ref = None
+    mine = None
+    for r in range(world):
+        a, b = orc.synth_inputs("ar", r, world, M, N, K, seed=seed)
+        p = a[rows].float() @ b.float()
+        ref = p if ref is None else ref + p
+        if r == rank:
+            mine, mine_partial = (a, b), p
+    A = mine[0].to(dev)
+    B = (mine[1] if layout == _lib.MK_B_KN else mine[1].t()).contiguous().to(dev)
+    C = mod.DistBuffer((M, N), dtype=torch.bfloat16, local_rank=rank, local_world_size=world,
+                       multicast=multicast)
+    Cf = mod.DistBuffer((M, N), dtype=torch.bfloat16, local_rank=rank, local_world_size=world,
+                        multicast=multicast)
+    barrier = mod.DistBuffer((2, 1024, 1024), dtype=torch.int32, local_rank=rank,
+                             local_world_size=world, multicast=multicast)
+    barrier.data_.zero_()
+    C.data_.zero_()
+    Cf.data_.zero_()
+    sync_all()
+    res = dict(op="ar", M=M, N=N, K=K, layout=layout, rel=[], rel_partial=[], status=[],
+               identical_across_ranks=[])
+    for it in range(iters):
+        mod.gemm_ar_intranode_blackwell(A, B, C, barrier, Cf, it + 1, layout)
+        torch.cuda.synchronize()
+        res["rel"].append(orc.rel_error(Cf.data_[rows.to(dev)].cpu(), ref))
+        res["rel_partial"].append(orc.rel_error(C.data_[rows.to(dev)].cpu(), mine_partial))
+        res["status"].append(list(mod.op_status(barrier)))
+        # every rank must hold bit-identical output (bench/common.py:469-500)
+        mine_bits = Cf.data_.view(torch.int16).cpu()
+        gathered = [None] * world
+        dist.all_gather_object(gathered, int(mine_bits.to(torch.int64).sum()))
+        res["identical_across_ranks"].append(len(set(gathered)) == 1)
+        Cf.data_.zero_()
+        sync_all()
+    return res
+
+
+CASES = {"ag": case_ag, "rs": case_rs, "ar": case_ar}
+
+
+def run_rank(rank: int, world: int, port: int, key: str, cases: list, out_dir: str, options=None):
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    os.environ["MKB200_BROKER_KEY"] = key
+    torch.cuda.set_device(rank)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    results = []
+    try:
+        for name, value in (options or {}).items():
+            _lib.set_option(name, value)
+        for c in cases:
+            c = dict(c)
+            fn = CASES[c.pop("op")]
+            results.append(fn(rank, world, **c))
+    except Exception:
+        results.append({"error": traceback.format_exc()})
+    Path(out_dir).mkdir(parents=True, exist_ok=True)
+    Path(out_dir, f"rank{rank}.json").write_text(json.dumps(results))
+    try:
+        dist.barrier()
+        dist.destroy_process_group()
+    except Exception:
+        pass
+
+
+if __name__ == "__main__":
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    cases = json.loads(os.environ.get("MKB200_CASES", "[]"))
+    run_rank(rank, world, int(os.environ.get("MASTER_PORT", "29700")),
+             os.environ.get("MKB200_BROKER_KEY", "manual"), cases,
+             os.environ.get("MKB200_OUT", "gpurun_out/multi"))

@@ -1,0 +1,85 @@
+"""Multi-GPU parity: one process per GPU on this box (2..8), every fused operator through the
+reference-shaped API against the CPU oracle.  Skipped when fewer than two GPUs are visible."""
+import json
+import os
+import tempfile
+import uuid
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from oracle import tp_gemm_oracle as orc
+from tests import multi_gpu_worker as worker
+
+pytestmark = pytest.mark.gpu
+
+
+def n_gpus():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def launch(world, cases, options=None, timeout=600):
+    out_dir = tempfile.mkdtemp(prefix="mkb200_mgpu_")
+    key = uuid.uuid4().hex[:12]
+    port = 29500 + (os.getpid() % 400)
+    ctx = mp.get_context("spawn")
+    procs = [ctx.Process(target=worker.run_rank, args=(r, world, port, key, cases, out_dir, options))
+             for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout)
+    alive = [p for p in procs if p.is_alive()]
+    for p in alive:
+        p.kill()
+    assert not alive, "a rank did not finish"
+    results = []
+    for r in range(world):
+        with open(os.path.join(out_dir, f"rank{r}.json")) as f:
+            results.append(json.load(f))
+    return results
+
+
+def check(results):
+    for rank, per_rank in enumerate(results):
+        for res in per_rank:
+            assert "error" not in res, res.get("error")
+            for st in res["status"]:
+                assert st[0] == 0, (rank, res)
+            assert max(res["rel"]) <= orc.REL_TOL, (rank, res)
+            if "gathered_exact" in res:
+                assert all(res["gathered_exact"]), (rank, res)
+            if "rel_partial" in res:
+                assert max(res["rel_partial"]) <= orc.REL_TOL, (rank, res)
+                assert all(res["identical_across_ranks"]), (rank, res)
+
+
+@pytest.mark.skipif(n_gpus() < 2, reason="needs at least 2 GPUs")
+def test_small_shapes_all_ops():
+    world = min(n_gpus(), 8)
+    world = 1 << (world.bit_length() - 1)
+    cases = [
+        dict(op="ag", M=world * 256, N=264, K=200, seed=1, iters=3, max_rows=4096),
+        dict(op="ag", M=world * 72, N=512, K=1024, seed=1, iters=2, max_rows=4096),
+        dict(op="rs", M=world * 256, N=512, K=192, seed=2, iters=3, max_rows=4096),
+        dict(op="rs", M=world * 128, N=264, K=72, seed=2, iters=2, max_rows=4096),
+        dict(op="ar", M=128, N=1024, K=256, seed=3, iters=3, max_rows=4096),
+        dict(op="ar", M=100, N=264, K=72, seed=3, iters=2, max_rows=4096, layout=0),
+        dict(op="ar", M=world * 128, N=512, K=128, seed=3, iters=2, max_rows=4096),
+    ]
+    check(launch(world, cases))
+
+
+@pytest.mark.skipif(n_gpus() < 2, reason="needs at least 2 GPUs")
+def test_baseline_shapes_sampled_rows():
+    """BASELINE configs 2-4 at their per-rank sizes, world = GPUs on this box; the oracle is
+    evaluated on sampled rows (the full CPU product would take minutes)."""
+    world = min(n_gpus(), 8)
+    world = 1 << (world.bit_length() - 1)
+    cases = [
+        dict(op="ag", M=8192, N=3584, K=8192, seed=1, iters=2, max_rows=16),
+        dict(op="rs", M=8192, N=8192, K=3584, seed=2, iters=2, max_rows=16),
+        dict(op="ar", M=128, N=8192, K=1024, seed=3, iters=3, max_rows=128),
+    ]
+    check(launch(world, cases, timeout=900))

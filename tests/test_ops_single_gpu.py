@@ -1,0 +1,146 @@
+"""The three operators through the reference-shaped Python API on one GPU (world size 1, where
+the exchange step is empty), checked against the CPU oracle; plus the bounded-wait path."""
+import ctypes
+
+import pytest
+import torch
+
+import mkernel_b200
+from mkernel_b200 import _lib
+from oracle import tp_gemm_oracle as orc
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def test_ag_gemm_world1():
+    mod = mkernel_b200.load("ag_gemm_warp_specialized")
+    M, N, K = 520, 264, 200        # ragged everywhere (M/W and N padded to 8 by the caller)
+    a, b_kn = orc.synth_inputs("ag", 0, 1, M, N, K, seed=1)
+    A = mod.DistBuffer((1, M, K), dtype=torch.bfloat16, local_rank=0, local_world_size=1,
+                       multicast=True)
+    A.data_[0].copy_(a)
+    ready = mod.DistBuffer((mod.ag_gemm_warp_specialized_ready_words,), dtype=torch.int32,
+                           local_rank=0, local_world_size=1, multicast=True)
+    ready.data_.zero_()
+    B = b_kn.t().contiguous().to(DEV)
+    C = torch.zeros((1, M, N), device=DEV, dtype=torch.bfloat16)
+    for _ in range(3):             # re-launch without host resets (epoch protocol)
+        C.zero_()
+        mod.ag_gemm_warp_specialized_prepare(ready, M, N)
+        mod.ag_gemm_warp_specialized_launch(A, ready, B, C)
+        torch.cuda.synchronize()
+        assert mod.op_status(ready)[0] == 0
+        a_full, ref = orc.ag_gemm_ref([a], b_kn)
+        assert torch.equal(A.data_.cpu().view(M, K), a_full)          # gathered operand: bit exact
+        assert orc.rel_error(C.cpu().view(M, N), ref) <= orc.REL_TOL
+    assert int(ready.data_[8]) == 3                                    # device epoch advanced
+    assert not A.multicast_enabled                                     # one device: no multicast
+
+
+def test_gemm_rs_world1_and_graph_replay():
+    mod = mkernel_b200.load("gemm_rs_blackwell")
+    M, N, K = 384, 512, 320
+    a, b_kn = orc.synth_inputs("rs", 0, 1, M, N, K, seed=2)
+    A = a.to(DEV)
+    B = b_kn.t().contiguous().to(DEV)
+    C = mod.DistBuffer((M, N), dtype=torch.bfloat16, local_rank=0, local_world_size=1, multicast=True)
+    sync = mod.DistBuffer(mod.gemm_rs_blackwell_sync_shape, dtype=torch.int32, local_rank=0,
+                          local_world_size=1, multicast=False)
+    mod.gemm_rs_blackwell_prepare(A, B, C, sync)
+    torch.cuda.synchronize()
+    mod.gemm_rs_blackwell_launch(A, B, C, sync)
+    torch.cuda.synchronize()
+    ref = orc.gemm_rs_ref([a], [b_kn])[0]
+    assert orc.rel_error(C.data_.cpu(), ref) <= orc.REL_TOL
+    # The reference's stale-state test (bench/gemm_rs_bench.py:226-242): capture one launch,
+    # replay it with A negated in between, never running prepare again.
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        mod.gemm_rs_blackwell_launch(A, B, C, sync)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=s):
+        mod.gemm_rs_blackwell_launch(A, B, C, sync)
+    sign = 1.0
+    for _ in range(3):
+        A.neg_()
+        sign = -sign
+        g.replay()
+        torch.cuda.synchronize()
+        assert orc.rel_error(C.data_.cpu(), sign * ref) <= orc.REL_TOL
+    assert mod.op_status(sync)[0] == 0
+    assert int(sync.data_[8]) == 5                                     # one epoch per executed launch
+
+
+@pytest.mark.parametrize("layout", [_lib.MK_B_KN, _lib.MK_B_NK])
+def test_gemm_ar_world1(layout):
+    mod = mkernel_b200.load("gemm_ar_blackwell")
+    M, N, K = 128, 1024, 256        # decode-shaped
+    a, b_kn = orc.synth_inputs("ar", 0, 1, M, N, K, seed=3)
+    A = a.to(DEV)
+    B = (b_kn if layout == _lib.MK_B_KN else b_kn.t()).contiguous().to(DEV)
+    C = mod.DistBuffer((M, N), dtype=torch.bfloat16, local_rank=0, local_world_size=1, multicast=True)
+    Cf = mod.DistBuffer((M, N), dtype=torch.bfloat16, local_rank=0, local_world_size=1, multicast=True)
+    barrier = mod.DistBuffer((2, 1024, 1024), dtype=torch.int32, local_rank=0, local_world_size=1,
+                             multicast=True)
+    barrier.data_.zero_()
+    total, partials = orc.gemm_ar_ref([a], [b_kn])
+    for epoch in (1, 2):
+        Cf.data_.zero_()
+        mod.gemm_ar_intranode_blackwell(A, B, C, barrier, Cf, epoch, layout)
+        torch.cuda.synchronize()
+        assert orc.rel_error(C.data_.cpu(), partials[0]) <= orc.REL_TOL     # local partial
+        assert orc.rel_error(Cf.data_.cpu(), total) <= orc.REL_TOL          # reduced output
+    # M outside the reference's {2048..32768} table is an ordinary case here, and epoch 0 is an error
+    with pytest.raises(RuntimeError):
+        mod.gemm_ar_intranode_blackwell(A, B, C, barrier, Cf, 0, layout)
+
+
+def test_shape_errors_raise():
+    mod = mkernel_b200.load("gemm_rs_blackwell")
+    A = torch.zeros((256, 64), device=DEV, dtype=torch.bfloat16)
+    B = torch.zeros((128, 72), device=DEV, dtype=torch.bfloat16)         # K mismatch
+    C = mod.DistBuffer((256, 128), dtype=torch.bfloat16, local_rank=0, local_world_size=1)
+    sync = mod.DistBuffer((4096,), dtype=torch.int32, local_rank=0, local_world_size=1)
+    with pytest.raises(RuntimeError):
+        mod.gemm_rs_blackwell_launch(A, B, C, sync)
+    with pytest.raises(RuntimeError):
+        mod.gemm_rs_blackwell_prepare(A, B, C, sync)                     # sync buffer too small
+
+
+def test_wait_that_nothing_satisfies_returns_a_status():
+    """Failure detection without a GPU fault: a two-rank reduce-scatter view is built by hand on
+    one GPU with a second 'rank' that never runs, so the tile flags of rank 1 are never raised.
+    The reduce role's wait must run out, record a status and let the kernel return; the context
+    stays usable."""
+    lib = _lib.lib()
+    M, N, K = 256, 256, 128
+    A = torch.randn((M, K), device=DEV).to(torch.bfloat16)
+    B = torch.randn((N, K), device=DEV).to(torch.bfloat16)
+    c = [torch.zeros((M, N), device=DEV, dtype=torch.bfloat16) for _ in range(2)]
+    s = [torch.zeros((_lib.MK_RS_SYNC_WORDS,), device=DEV, dtype=torch.int32) for _ in range(2)]
+
+    def view(bufs):
+        v = _lib.SymmView()
+        v.rank, v.world, v.bytes = 0, 2, bufs[0].numel() * bufs[0].element_size()
+        v.peer[0], v.peer[1] = bufs[0].data_ptr(), bufs[1].data_ptr()
+        return v
+
+    cv, sv = view(c), view(s)
+    _lib.set_option("wait_limit_ms", 300)
+    try:
+        rc = lib.mk_gemm_rs_launch(A.data_ptr(), B.data_ptr(), ctypes.byref(cv), ctypes.byref(sv),
+                                   M, N, K, None)
+        assert rc == 0, _lib.last_error()
+        torch.cuda.synchronize()                                        # returns: the wait is bounded
+    finally:
+        _lib.set_option("wait_limit_ms", 4000)
+    out = (ctypes.c_uint32 * 4)()
+    rc = lib.mk_op_status(ctypes.byref(sv), out)
+    assert rc == -5 and out[0] in (3, 4), (rc, list(out))               # tile flag / exit handshake
+    assert "device wait expired" in _lib.last_error()
+    # the partial product was still computed, and the device still works
+    assert orc.rel_error(c[0][128:].cpu(), (A.float() @ B.float().t())[128:].cpu()) <= orc.REL_TOL
+    assert torch.equal(torch.ones(4, device=DEV) * 2, torch.full((4,), 2.0, device=DEV))
