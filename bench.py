@@ -1,0 +1,478 @@
+#!/usr/bin/env python
+"""Benchmark of the fused tensor-parallel GEMM + collective operators on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+
+Headline workload (one "step" = one entry barrier + one fused launch): AllGather+GEMM at the
+Llama-70B MLP up-projection shape with tensor parallel degree = N: every rank holds an A shard
+[8192/N, 8192] and its column shard of B [8192 -> 3584], and produces C [8192, 3584] (bf16 in,
+fp32 accumulate, bf16 out).  Work per GPU is fixed (481 GFLOP), so scaling is weak.  The same
+run also times GEMM+ReduceScatter (down-projection shape) and GEMM+AllReduce (decode shape) and
+their unfused cuBLAS(+NCCL) counterparts and reports them under "ops".
+
+Prints ONE JSON line on rank 0.  `--impl reference` times the reference's CPU path
+(torch.matmul on the host cores over a bounded sample of the same workload) instead.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+CFG2 = dict(M=8192, N=3584, K=8192)          # AllGather+GEMM (headline), N is per rank
+CFG3 = dict(M=8192, N=8192, K=3584)          # GEMM+ReduceScatter, K is per rank
+CFG4 = dict(M=128, N=8192, K=1024)           # GEMM+AllReduce decode shape, K is per rank
+NVLINK_GBS = 900.0                           # per direction per GPU (nominal, per BASELINE)
+FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0)
+
+# dram__bytes_read.sum + dram__bytes_write.sum of one fused launch at the headline shape on one
+# GPU, from the ncu capture summarised under profiles/ (None until a capture exists).
+NCU_TRAFFIC_BYTES_PER_LAUNCH = None
+
+
+def load_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return dict(hbm_gbs=d["hbm_gbs"], bf16_tflops=d["bf16_tflops"],
+                    bf16_tflops_sustained=d.get("bf16_tflops_sustained", d["bf16_tflops"])), "measured"
+    return dict(FALLBACK_PEAKS), "fallback"
+
+
+# ------------------------------------------------------------------------------------------------
+# clocks
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while a region runs."""
+
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown",
+               0x4: "sw_power_cap"}
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _run(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                for bit, name in self.REASONS.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            time.sleep(0.002)
+
+    def __enter__(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(1.0)
+
+    def summary(self):
+        s = sorted(self.samples)
+        return {"sm_mhz": s[len(s) // 2] if s else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+# ------------------------------------------------------------------------------------------------
+# distributed plumbing
+# ------------------------------------------------------------------------------------------------
+class Dist:
+    def __init__(self, n_gpus: int):
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        if self.world != n_gpus:
+            if self.world == 1 and n_gpus > 1:
+                raise SystemExit(f"--gpus {n_gpus} needs a torchrun launch with {n_gpus} ranks")
+            n_gpus = self.world
+        self.dist = None
+        if self.world > 1:
+            import torch.distributed as dist
+            os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+            torch.cuda.set_device(self.local_rank)
+            dist.init_process_group("nccl", device_id=torch.device("cuda", self.local_rank))
+            self.dist = dist
+        else:
+            torch.cuda.set_device(0)
+        self.device = torch.device("cuda", self.local_rank)
+
+    def barrier(self):
+        torch.cuda.synchronize()
+        if self.dist is not None:
+            self.dist.barrier()
+            torch.cuda.synchronize()
+
+    def max_over_ranks(self, value: float) -> float:
+        if self.dist is None:
+            return value
+        t = torch.tensor([value], dtype=torch.float64, device=self.device)
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+
+def timed_loop(dst: Dist, step, steps: int, warmup: int, sampler=None):
+    """Warm up, then time exactly `steps` calls of step(i, ev0, ev1) with CUDA events on the
+    current stream between two barriers.  step records ev0/ev1 around its fused launch.
+    Returns (total ms max over ranks, mean fused-launch ms max over ranks)."""
+    evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+           for _ in range(steps)]
+    null = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+    for i in range(warmup):
+        step(i, *null)
+    dst.barrier()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    ctx = sampler if sampler is not None else _Null()
+    with ctx:
+        t0.record()
+        for i in range(steps):
+            step(warmup + i, *evs[i])
+        t1.record()
+        torch.cuda.synchronize()
+    dst.barrier()
+    total = dst.max_over_ranks(t0.elapsed_time(t1))
+    kern = dst.max_over_ranks(sum(a.elapsed_time(b) for a, b in evs) / steps)
+    return total, kern
+
+
+class _Null:
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        return False
+
+
+def randn_bf16(shape, seed, device, scale=1.0):
+    g = torch.Generator(device=device).manual_seed(seed)
+    return (torch.randn(shape, device=device, generator=g) * scale).to(torch.bfloat16)
+
+
+# ------------------------------------------------------------------------------------------------
+# our arm
+# ------------------------------------------------------------------------------------------------
+def run_ours(args):
+    import mkernel_b200
+    from mkernel_b200 import _lib, ops
+
+    dst = Dist(args.gpus)
+    W, rank, dev = dst.world, dst.local_rank, dst.device
+    peaks, peak_kind = load_peaks()
+    steps, warmup = args.steps, max(args.warmup, 3)
+
+    # ---------------- headline: AllGather + GEMM ----------------
+    M, N, K = CFG2["M"], CFG2["N"], CFG2["K"]
+    Ms = M // W
+    ag = mkernel_b200.load("ag_gemm_warp_specialized")
+    A = ag.DistBuffer((W, Ms, K), dtype=torch.bfloat16, local_rank=rank, local_world_size=W)
+    ready = ag.DistBuffer((ag.ag_gemm_warp_specialized_ready_words,), dtype=torch.int32,
+                          local_rank=rank, local_world_size=W)
+    ready.data_.zero_()
+    A.data_.zero_()
+    A.data_[rank].copy_(randn_bf16((Ms, K), 1 + rank, dev))
+    B = randn_bf16((N, K), 101 + rank, dev, K ** -0.5)      # stored [N, K] as the operator takes it
+    C = torch.zeros((W, Ms, N), device=dev, dtype=torch.bfloat16)
+    dst.barrier()
+
+    def ag_step(i, e0, e1):
+        ag.ag_gemm_warp_specialized_prepare(ready, M, N)
+        e0.record()
+        ag.ag_gemm_warp_specialized_launch(A, ready, B, C)
+        e1.record()
+
+    sampler = ClockSampler(rank)
+    total_ms, kern_ms = timed_loop(dst, ag_step, steps, warmup, sampler)
+    ag.op_status(ready)
+    flops_per_gpu = 2.0 * M * N * K
+    ms_per_step = total_ms / steps
+    value = W * flops_per_gpu / (ms_per_step * 1e-3) / 1e12
+    achieved = flops_per_gpu / (kern_ms * 1e-3) / 1e12
+    ag_bytes = (W - 1) / W * M * K * 2
+    t_roof_ms = max(flops_per_gpu / (peaks["bf16_tflops"] * 1e12), ag_bytes / (NVLINK_GBS * 1e9)) * 1e3
+
+    # ---------------- end to end through the public API, host buffers ----------------
+    hA = randn_bf16((Ms, K), 1 + rank, "cpu").pin_memory()
+    hB = B.cpu().pin_memory()
+    hC = torch.empty((W, Ms, N), dtype=torch.bfloat16).pin_memory()
+    dB = torch.empty_like(B)
+
+    def e2e_step(i, e0, e1):
+        A.data_[rank].copy_(hA, non_blocking=True)
+        dB.copy_(hB, non_blocking=True)
+        ag.ag_gemm_warp_specialized_prepare(ready, M, N)
+        ag.ag_gemm_warp_specialized_launch(A, ready, dB, C)
+        hC.copy_(C, non_blocking=True)
+
+    e2e_steps = max(3, min(steps, 10))
+    e2e_total, _ = timed_loop(dst, e2e_step, e2e_steps, 3)
+    e2e_value = W * flops_per_gpu / (e2e_total / e2e_steps * 1e-3) / 1e12
+    h2d = hA.numel() * 2 + hB.numel() * 2
+    d2h = hC.numel() * 2
+
+    # ---------------- unfused comparator for the headline ----------------
+    ops_out = {}
+    A_full = torch.empty((M, K), device=dev, dtype=torch.bfloat16)
+    A_loc = A.data_[rank]
+    C2 = torch.empty((M, N), device=dev, dtype=torch.bfloat16)
+
+    def ag_unfused(i, e0, e1):
+        e0.record()
+        if W > 1:
+            dst.dist.all_gather_into_tensor(A_full, A_loc)
+            torch.matmul(A_full, B.t(), out=C2)
+        else:
+            torch.matmul(A_loc, B.t(), out=C2)
+        e1.record()
+
+    sub_steps = max(5, min(steps, 20))
+    _, ag_unf_ms = timed_loop(dst, ag_unfused, sub_steps, 3)
+    ops_out["ag_gemm"] = op_record("AllGather+GEMM", CFG2, W, kern_ms, ag_unf_ms, flops_per_gpu,
+                                   ag_bytes, peaks)
+    del A_full, C2, hA, hB, hC, dB
+
+    # ---------------- GEMM + ReduceScatter (config 3) ----------------
+    M3, N3, K3 = CFG3["M"], CFG3["N"], CFG3["K"]
+    rs = mkernel_b200.load("gemm_rs_blackwell")
+    A3 = randn_bf16((M3, K3), 2 + rank, dev)
+    B3 = randn_bf16((N3, K3), 202 + rank, dev, (K3 * W) ** -0.5)
+    C3 = rs.DistBuffer((M3, N3), dtype=torch.bfloat16, local_rank=rank, local_world_size=W)
+    sync3 = rs.DistBuffer(rs.gemm_rs_blackwell_sync_shape, dtype=torch.int32, local_rank=rank,
+                          local_world_size=W)
+    rs.gemm_rs_blackwell_prepare(A3, B3, C3, sync3)
+    dst.barrier()
+
+    def rs_step(i, e0, e1):
+        e0.record()
+        rs.gemm_rs_blackwell_launch(A3, B3, C3, sync3)
+        e1.record()
+
+    _, rs_ms = timed_loop(dst, rs_step, sub_steps, 3)
+    rs.op_status(sync3)
+    c3 = torch.empty((M3, N3), device=dev, dtype=torch.bfloat16)
+    c3_rs = torch.empty((M3 // W, N3), device=dev, dtype=torch.bfloat16)
+
+    def rs_unfused(i, e0, e1):
+        e0.record()
+        torch.mm(A3, B3.t(), out=c3)
+        if W > 1:
+            dst.dist.reduce_scatter_tensor(c3_rs, c3)
+        e1.record()
+
+    _, rs_unf_ms = timed_loop(dst, rs_unfused, sub_steps, 3)
+    ops_out["gemm_rs"] = op_record("GEMM+ReduceScatter", CFG3, W, rs_ms, rs_unf_ms,
+                                   2.0 * M3 * N3 * K3, (W - 1) / W * M3 * N3 * 2, peaks)
+    del c3, c3_rs
+    C3.free(); sync3.free()
+
+    # ---------------- GEMM + AllReduce (config 4, decode shape) ----------------
+    M4, N4, K4 = CFG4["M"], CFG4["N"], CFG4["K"]
+    ar = mkernel_b200.load("gemm_ar_blackwell")
+    A4 = randn_bf16((M4, K4), 3 + rank, dev)
+    B4 = randn_bf16((K4, N4), 303 + rank, dev, (K4 * W) ** -0.5)
+    C4 = ar.DistBuffer((M4, N4), dtype=torch.bfloat16, local_rank=rank, local_world_size=W)
+    C4f = ar.DistBuffer((M4, N4), dtype=torch.bfloat16, local_rank=rank, local_world_size=W)
+    bar4 = ar.DistBuffer((2, 1024, 1024), dtype=torch.int32, local_rank=rank, local_world_size=W)
+    bar4.data_.zero_()
+    dst.barrier()
+
+    def ar_step(i, e0, e1):
+        e0.record()
+        ar.gemm_ar_intranode_blackwell(A4, B4, C4, bar4, C4f, i + 1)
+        e1.record()
+
+    ar_steps = max(20, sub_steps)
+    _, ar_ms = timed_loop(dst, ar_step, ar_steps, 5)
+    ar.op_status(bar4)
+    c4 = torch.empty((M4, N4), device=dev, dtype=torch.bfloat16)
+
+    def ar_unfused(i, e0, e1):
+        e0.record()
+        torch.matmul(A4, B4, out=c4)
+        if W > 1:
+            dst.dist.all_reduce(c4)
+        e1.record()
+
+    _, ar_unf_ms = timed_loop(dst, ar_unfused, ar_steps, 5)
+    rec = op_record("GEMM+AllReduce (decode)", CFG4, W, ar_ms, ar_unf_ms, 2.0 * M4 * N4 * K4,
+                    M4 * N4 * 2 if W > 1 else 0, peaks)
+    hbm_bytes = (M4 * K4 + K4 * N4 + 2 * M4 * N4) * 2
+    rec["fused_us"] = ar_ms * 1e3
+    rec["hbm_floor_us"] = hbm_bytes / (peaks["hbm_gbs"] * 1e9) * 1e6
+    ops_out["gemm_ar"] = rec
+
+    line = {
+        "metric": "fused AG-GEMM TFLOPS (whole job; GEMM-RS / GEMM-AR under ops)",
+        "value": value, "unit": "TFLOP/s", "per_gpu": value / W,
+        "n_gpus": W, "steps": steps, "warmup": warmup, "ms_per_step": ms_per_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "AllGather+GEMM, Llama-70B MLP up-proj, TP=n_gpus: A shard "
+                               f"[{Ms},{K}] x B [{K},{N}] -> C [{M},{N}] per GPU",
+                   "M": M, "N_per_gpu": N, "K": K, "tp": W,
+                   "l2": "operands 246 MB per GPU exceed the 126 MB L2; no flush between steps",
+                   "step": "entry barrier kernel + one fused persistent kernel"},
+        "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"],
+                     "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
+                     "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"],
+                     "peak_source": f"{peak_kind} (burst cuBLAS bf16)",
+                     "kernel_ms": kern_ms, "fused_roofline_ms": t_roof_ms,
+                     "fused_roofline_frac": t_roof_ms / kern_ms,
+                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH},
+        "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_total / e2e_steps},
+        "gpu_launches": 2 * steps,
+        "clocks": sampler.summary(),
+        "ops": ops_out,
+        "plan": plan_summary(_lib, W, rank),
+    }
+    if W == 1:
+        line["cpu_baseline"] = cpu_baseline(CFG2, 1, budget_s=10.0)
+    if dst.rank == 0:
+        print(json.dumps(line), flush=True)
+    dst.barrier()
+    if dst.dist is not None:
+        dst.dist.destroy_process_group()
+
+
+def plan_summary(_lib, W, rank):
+    out = {}
+    for name, op, cfg, layout in (("ag_gemm", _lib.OP_AG, CFG2, 0), ("gemm_rs", _lib.OP_RS, CFG3, 0),
+                                  ("gemm_ar", _lib.OP_AR, CFG4, 1)):
+        p = _lib.plan_op(op, rank, W, cfg["M"], cfg["N"], cfg["K"], layout,
+                         torch.cuda.get_device_properties(rank).multi_processor_count)
+        out[name] = {"block_n": p.block_n, "stages": p.stages, "exchange_ctas": p.n_comm,
+                     "grid": p.grid}
+    return out
+
+
+def op_record(name, cfg, W, fused_ms, unfused_ms, flops, nvlink_bytes, peaks):
+    t_roof = max(flops / (peaks["bf16_tflops"] * 1e12), nvlink_bytes / (NVLINK_GBS * 1e9)) * 1e3
+    return {"name": name, "shape": cfg, "tp": W, "fused_ms": fused_ms, "unfused_ms": unfused_ms,
+            "tflops_per_gpu": flops / (fused_ms * 1e-3) / 1e12,
+            "unfused_tflops_per_gpu": flops / (unfused_ms * 1e-3) / 1e12,
+            "speedup_vs_unfused": unfused_ms / fused_ms,
+            "fused_roofline_ms": t_roof, "fused_roofline_frac": t_roof / fused_ms,
+            "nvlink_bytes_per_gpu": nvlink_bytes}
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU baseline / reference arm: the reference's torch path on the host cores
+# ------------------------------------------------------------------------------------------------
+def cpu_sample(cfg, W, rows, literal=False):
+    """One bounded sample of the headline workload on the CPU: gather W shards and multiply
+    `rows` rows of the gathered A by B.  literal=False: the oracle (fp32 product of the bf16
+    operands).  literal=True: the reference's own calls on CPU tensors -- concatenation as
+    all_gather_into_tensor produces it, then torch.mm on the bf16 tensors
+    (bench/ag_gemm_bench.py:567-568)."""
+    from oracle import tp_gemm_oracle as orc
+    K, N = cfg["K"], cfg["N"]
+    g = torch.Generator().manual_seed(1)
+    per = max(1, rows // W)
+    shards = [torch.randn((per, K), generator=g).to(torch.bfloat16) for _ in range(W)]
+    b_kn = (torch.randn((K, N), generator=g) * K ** -0.5).to(torch.bfloat16)
+    t0 = time.perf_counter()
+    if literal:
+        c = torch.mm(torch.cat(shards, 0), b_kn)
+    else:
+        _, c = orc.ag_gemm_ref(shards, b_kn)
+    dt = time.perf_counter() - t0
+    return 2.0 * per * W * N * K, dt, float(c[0, 0])
+
+
+def cpu_baseline(cfg, W, budget_s):
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    flops, dt, _ = cpu_sample(cfg, W, 64)               # calibration
+    rate = flops / max(dt, 1e-6)
+    rows = int(min(cfg["M"], max(64, budget_s * rate / (2.0 * cfg["N"] * cfg["K"]))))
+    rows = max(W, rows // W * W)
+    flops, dt, _ = cpu_sample(cfg, W, rows)
+    return {"value": flops / dt / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
+            "kind": "port",
+            "sample": f"{rows} of {cfg['M']} gathered rows x N={cfg['N']} x K={cfg['K']}, "
+                      f"fp32 torch.matmul on bf16-rounded operands ({dt:.2f} s)"}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    W = int(os.environ.get("WORLD_SIZE", "1"))
+    if rank != 0:
+        return
+    steps, warmup = args.steps, args.warmup
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    cfg = CFG2
+    budget = min(3.0, 120.0 / max(1, steps + warmup))   # whole run within a few minutes
+    flops, dt, _ = cpu_sample(cfg, W, 256, literal=True)
+    rate = flops / max(dt, 1e-6)
+    rows = int(min(cfg["M"], max(64, budget * rate / (2.0 * cfg["N"] * cfg["K"]))))
+    rows = max(W, rows // W * W)
+    for _ in range(warmup):
+        cpu_sample(cfg, W, rows, literal=True)
+    t_total, f_total = 0.0, 0.0
+    for _ in range(steps):
+        f, dt, _ = cpu_sample(cfg, W, rows, literal=True)
+        t_total += dt
+        f_total += f
+    value = f_total / t_total / 1e12
+    sample = (f"{rows} of {cfg['M']} gathered rows per step x N={cfg['N']} x K={cfg['K']}; "
+              "torch.cat + torch.mm on bf16 CPU tensors (the reference's check path run on the host)")
+    line = {
+        "impl": "reference",
+        "metric": "fused AG-GEMM TFLOPS (whole job; GEMM-RS / GEMM-AR under ops)",
+        "value": value, "unit": "TFLOP/s", "n_gpus": W, "steps": steps, "warmup": warmup,
+        "ms_per_step": t_total / steps * 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "AllGather+GEMM, Llama-70B MLP up-proj, TP=n_gpus (bounded sample)",
+                   "M": cfg["M"], "N_per_gpu": cfg["N"], "K": cfg["K"], "tp": W},
+        "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
+                         "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
