@@ -1,13 +1,16 @@
 // One persistent sm_100a kernel for the tensor-parallel GEMM + collective operators.
 //
 // CTA roles (fixed for the lifetime of the kernel, chosen by blockIdx.x):
-//   exchange CTAs [0, n_comm)  AllGather: pull peers' A rows into the local gathered buffer with
-//                              untiled bulk copies (peer global -> shared -> local global) and raise
-//                              one flag per 16-row group.
-//                              ReduceScatter / AllReduce: wait until every rank has raised the
-//                              flags of a row-block this rank owns, sum the W partial copies
-//                              (fp32 accumulate, fixed rank order) and write the bf16 result
-//                              locally (RS) or to every rank's output (AR).
+//   exchange CTAs [0, n_comm)  AllGather: push this rank's A rows into every peer's gathered buffer
+//                              with posted remote stores (or one NVSwitch multicast store) and
+//                              raise one flag per 16-row group on the receiver.
+//                              ReduceScatter: GEMM tiles are stored straight into the owner's
+//                              buffer (slab = producing rank); the owner waits for the flags of
+//                              a row-block, sums its W local slabs (fp32 accumulate, fixed rank
+//                              order) and writes the bf16 result in place.
+//                              AllReduce: as ReduceScatter but partials stay with their producer
+//                              and are fetched by the owner, which then stores the result into
+//                              every rank's output.
 //   compute CTAs  [n_comm, G)  bf16 GEMM tiles of 128 x block_n: warp 0 feeds a shared-memory ring
 //                              with TMA tile loads, warp 1 issues tcgen05.mma into one of two TMEM
 //                              accumulators, warps 4-7 drain the other accumulator (tcgen05.ld ->
@@ -145,11 +148,11 @@ __device__ __forceinline__ void compute_cta(const CUtensorMap* tma_a, const CUte
         bool mine = true;
         if (lane < kGatherSub) {
           const uint32_t* f = p.sync + SW_FLAGS + gather_flag_index(ti.rowblock, lane);
-          mine = bounded_wait<true>(wc, [&] { return ptx::ld_acquire_gpu(f) == epoch; },
+          mine = bounded_wait<true>(wc, [&] { return ptx::ld_acquire_sys(f) == epoch; },
                                     ST_TIMEOUT_GATHER, ti.rowblock, lane);
         }
         ok = __all_sync(0xffffffffu, mine);
-        ptx::fence_proxy_async();  // gathered rows were written through another proxy
+        ptx::fence_proxy_async();  // rows stored by a peer GPU are about to be read by TMA
         if (!ok) break;
       }
       if (lane == 0) {
@@ -244,6 +247,19 @@ __device__ __forceinline__ void compute_cta(const CUtensorMap* tma_a, const CUte
       const int r_in_tile = quarter * 32 + lane;
       const bool row_ok = r_in_tile < ti.rows;
       __nv_bfloat16* crow = C + static_cast<long long>(ti.row0 + r_in_tile) * p.ldc;
+      __nv_bfloat16* crow2 = nullptr;  // second destination (AllReduce on one GPU: C_final)
+      if (OP == OP_RS && s.world > 1 && row_ok) {
+        // ReduceScatter: the row belongs to owner o; store it straight into o's buffer, in the
+        // slab reserved for this (producing) rank.  Remote when o != rank: a posted NVLink write.
+        const int grow = ti.row0 + r_in_tile;
+        const int o = grow / s.part_rows;
+        const int i = grow - o * s.part_rows;
+        crow = static_cast<__nv_bfloat16*>(p.peer_data[o]) +
+               static_cast<long long>(s.rank * s.part_rows + i) * p.ldc;
+      }
+      if (OP == OP_AR && s.world == 1)
+        crow2 = static_cast<__nv_bfloat16*>(p.peer_out[0]) +
+                static_cast<long long>(ti.row0 + r_in_tile) * p.ldc;
       const uint32_t t_base = tmem_base + acc * 256 + (static_cast<uint32_t>(quarter * 32) << 16);
       for (int c = 0; c < bn; c += 32) {
         uint32_t r[32];
@@ -260,6 +276,7 @@ __device__ __forceinline__ void compute_cta(const CUtensorMap* tma_a, const CUte
               v.z = ptx::pack_bf16x2(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5]));
               v.w = ptx::pack_bf16x2(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7]));
               ptx::st_global_v4(crow + col + g * 8, v);
+              if (OP == OP_AR && crow2 != nullptr) ptx::st_global_v4(crow2 + col + g * 8, v);
             }
           }
         }
@@ -277,116 +294,66 @@ __device__ __forceinline__ void compute_cta(const CUtensorMap* tma_a, const CUte
 }
 
 // ------------------------------------------------------------------------------------------
-// Exchange CTA: AllGather pull
+// Exchange CTA: AllGather push
 // ------------------------------------------------------------------------------------------
-struct GatherCursor {
-  // Walks the 16-row groups assigned to this CTA and the 16 KiB chunks inside each group.
-  int x, x_end, stride;  // item index: ((d-1) * part_blocks + j) * kGatherSub + g
-  int chunk, n_chunks;
-  long long bytes, offset;  // of the current item inside the gathered buffer
-  int rowblock, sub;
-};
-
-__device__ __forceinline__ void gather_load_item(const OpParams& p, GatherCursor& c) {
+// Every rank writes its own shard into the gathered buffer of every peer with posted remote
+// stores (a pull would pay one NVLink round trip per request and is latency-bound per SM).
+// Work items are 16-row groups of the own shard.  Peer-to-peer: items are ordered peer-major,
+// nearest deadline first -- rank r's shard is needed first by rank r-1 (ring distance 1 from its
+// point of view), then r-2, ... -- and dealt round-robin to the exchange CTAs so that all of them
+// serve the same peer at a time.  NVSwitch multicast: one multimem store lands in every replica,
+// so there is a single pass over the shard.  After the stores of a group: CTA barrier, one
+// system-scope fence, then the group's flag is written on the receiving rank(s).
+__device__ __forceinline__ void gather_push_cta(const OpParams& p, WaitCtx& wc, uint32_t epoch) {
   const Sched& s = p.sched;
-  {
-    const int g = c.x % kGatherSub;
-    const int bj = c.x / kGatherSub;
-    const int d = 1 + bj / s.part_blocks, j = bj % s.part_blocks;
-    const int src = (s.rank + d) % s.world;
-    c.rowblock = src * s.part_blocks + j;
-    c.sub = g;
-    const int rows_in_block = rowblock_rows(s, c.rowblock);
+  const int tid = threadIdx.x;
+  const int W = s.world;
+  wc.where = (blockIdx.x << 8) | 8u;
+  const bool nvls = p.use_nvls && p.mc_data != nullptr;
+  const int groups = s.part_blocks * kGatherSub;          // 16-row groups in one shard
+  const int n_items = nvls ? groups : (W - 1) * groups;
+  const char* local = static_cast<const char*>(p.peer_data[s.rank]);
+  const long long row_bytes = static_cast<long long>(p.K) * 2;
+
+  for (int x = blockIdx.x; x < n_items; x += p.n_comm) {
+    const int d = nvls ? 0 : 1 + x / groups;               // ring distance of the receiving rank
+    const int jg = x % groups;
+    const int j = jg / kGatherSub, g = jg % kGatherSub;
+    const int rowblock = s.rank * s.part_blocks + j;
+    const int rows_in_block = rowblock_rows(s, rowblock);
     const int r0 = g * (kBlockM / kGatherSub);
     int r1 = r0 + kBlockM / kGatherSub;
     if (r1 > rows_in_block) r1 = rows_in_block;
-    const int nrows = r1 > r0 ? r1 - r0 : 0;
-    c.bytes = static_cast<long long>(nrows) * p.K * 2;
-    c.offset = (static_cast<long long>(rowblock_row0(s, c.rowblock)) + r0) * p.K * 2;
-    c.n_chunks = static_cast<int>((c.bytes + kGatherChunk - 1) / kGatherChunk);
-    c.chunk = 0;
-  }
-}
-__device__ __forceinline__ bool gather_valid(const GatherCursor& c) { return c.x < c.x_end; }
-// Advance by one chunk; items without rows have n_chunks == 0 and are skipped by the caller.
-__device__ __forceinline__ void gather_advance(const OpParams& p, GatherCursor& c) {
-  if (++c.chunk >= c.n_chunks) {
-    c.x += c.stride;
-    if (c.x < c.x_end) gather_load_item(p, c);
-  }
-}
-
-__device__ __forceinline__ void gather_cta(const OpParams& p, uint32_t smem_base,
-                                           uint32_t bar_base, WaitCtx& wc, uint32_t epoch,
-                                           int ring_bytes) {
-  if (threadIdx.x != 0) return;
-  const Sched& s = p.sched;
-  wc.where = (blockIdx.x << 8) | 8u;
-  int ns = ring_bytes / kGatherChunk;
-  if (ns > 24) ns = 24;
-  auto bar = [&](int slot) { return bar_base + 8u * slot; };
-  const int n_items = (s.world - 1) * s.part_blocks * kGatherSub;
-
-  GatherCursor ld, st;
-  ld.x = blockIdx.x; ld.x_end = n_items; ld.stride = p.n_comm;
-  ld.n_chunks = 0; ld.chunk = 0;
-  if (gather_valid(ld)) gather_load_item(p, ld);
-  st = ld;
-  uint32_t* flags = p.sync + SW_FLAGS;
-
-  // Row groups that have no rows (ragged last block) are flagged straight away.
-  auto skip_empty = [&](GatherCursor& c, bool flag_it) {
-    while (gather_valid(c) && c.n_chunks == 0) {
-      if (flag_it) ptx::st_release_gpu(flags + gather_flag_index(c.rowblock, c.sub), epoch);
-      c.x += c.stride;
-      if (gather_valid(c)) gather_load_item(p, c);
+    const long long bytes = r1 > r0 ? (r1 - r0) * row_bytes : 0;
+    const long long base = (static_cast<long long>(rowblock_row0(s, rowblock)) + r0) * row_bytes;
+    const int dst_rank = (s.rank - d + W) % W;
+    char* dst = nvls ? static_cast<char*>(p.mc_data) : static_cast<char*>(p.peer_data[dst_rank]);
+    const long long stride = static_cast<long long>(kThreads) * 16;
+    for (long long off = static_cast<long long>(tid) * 16; off < bytes; off += 4 * stride) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (off + u * stride < bytes) v[u] = ptx::ld_global_v4_stream(local + base + off + u * stride);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (off + u * stride < bytes) {
+          if (nvls) ptx::multimem_st_v4(dst + base + off + u * stride, v[u]);
+          else ptx::st_global_v4(dst + base + off + u * stride, v[u]);
+        }
+      }
     }
-  };
-  skip_empty(ld, false);
-  skip_empty(st, true);
-
-  long long l = 0, sidx = 0;  // ring positions of the next load / next store
-  while (gather_valid(st)) {
-    while (gather_valid(ld) && l <= sidx - 2 + ns) {
-      const int slot = static_cast<int>(l % ns);
-      const long long off = ld.offset + static_cast<long long>(ld.chunk) * kGatherChunk;
-      long long nb = ld.bytes - static_cast<long long>(ld.chunk) * kGatherChunk;
-      if (nb > kGatherChunk) nb = kGatherChunk;
-      const int src = rowblock_shard(s, ld.rowblock);
-      ptx::mbar_expect_tx(bar(BAR_SLOT + slot), static_cast<uint32_t>(nb));
-      ptx::bulk_g2s(smem_base + slot * kGatherChunk,
-                    static_cast<const char*>(p.peer_data[src]) + off, static_cast<uint32_t>(nb),
-                    bar(BAR_SLOT + slot));
-      gather_advance(p, ld);
-      skip_empty(ld, false);
-      ++l;
+    __syncthreads();
+    if (tid == 0) {
+      ptx::fence_acq_rel_sys();
+      const long long idx = SW_FLAGS + gather_flag_index(rowblock, g);
+      if (nvls) {
+        for (int r = 0; r < W; ++r)
+          if (r != s.rank) ptx::st_relaxed_sys(p.peer_sync[r] + idx, epoch);
+      } else {
+        ptx::st_relaxed_sys(p.peer_sync[dst_rank] + idx, epoch);
+      }
     }
-    const int slot = static_cast<int>(sidx % ns);
-    const uint32_t parity = static_cast<uint32_t>((sidx / ns) & 1);
-    if (!bounded_wait<false>(wc, [&] { return ptx::mbar_try_wait(bar(BAR_SLOT + slot), parity); },
-                             ST_TIMEOUT_COPY, st.rowblock, st.sub))
-      return;
-    const long long off = st.offset + static_cast<long long>(st.chunk) * kGatherChunk;
-    long long nb = st.bytes - static_cast<long long>(st.chunk) * kGatherChunk;
-    if (nb > kGatherChunk) nb = kGatherChunk;
-    ptx::bulk_s2g(static_cast<char*>(p.peer_data[s.rank]) + off, smem_base + slot * kGatherChunk,
-                  static_cast<uint32_t>(nb));
-    ptx::bulk_commit();
-    if (st.chunk + 1 >= st.n_chunks) {
-      // Last chunk of a 16-row group: wait until every store of the group has been written,
-      // then publish the group to the compute CTAs of this GPU.
-      ptx::bulk_wait_all<0>();
-      ptx::fence_proxy_async();
-      __threadfence();
-      ptx::st_release_gpu(flags + gather_flag_index(st.rowblock, st.sub), epoch);
-    } else {
-      ptx::bulk_wait_read<1>();
-    }
-    gather_advance(p, st);
-    skip_empty(st, true);
-    ++sidx;
   }
-  ptx::bulk_wait_all<0>();
 }
 
 // ------------------------------------------------------------------------------------------
@@ -417,7 +384,14 @@ __device__ __forceinline__ void reduce_cta(const OpParams& p, uint32_t smem_base
   const int n_items = owner_num_items(s, s.rank);
   const int first_block = owner_first_block(s, s.rank);
   const long long row_bytes = static_cast<long long>(s.N) * 2;
-  const bool nvls = p.use_nvls && p.mc_data != nullptr && (OP == OP_RS || p.mc_out != nullptr);
+  // ReduceScatter sums W slabs of its own buffer; AllReduce fetches every rank's partial.
+  const bool nvls = OP == OP_AR && p.use_nvls && p.mc_data != nullptr && p.mc_out != nullptr;
+  char* const local = static_cast<char*>(p.peer_data[s.rank]);
+  auto src_base = [&](int src) -> const char* {
+    if (OP == OP_RS)
+      return local + (static_cast<long long>(src) - s.rank) * s.part_rows * row_bytes;
+    return static_cast<const char*>(p.peer_data[src]);
+  };
   long long pos = 0;  // ring position, continues across items
 
   for (int k = 0; k < n_items; ++k) {
@@ -465,8 +439,7 @@ __device__ __forceinline__ void reduce_cta(const OpParams& p, uint32_t smem_base
         for (int u = 0; u < 4; ++u) {
           if (!have[u]) continue;
           const long long off = base + chunk_off(i0 + u) + tid * 16;
-          if (OP == OP_RS) ptx::st_global_v4(static_cast<char*>(p.peer_data[s.rank]) + off, v[u]);
-          else ptx::multimem_st_v4(static_cast<char*>(p.mc_out) + off, v[u]);
+          ptx::multimem_st_v4(static_cast<char*>(p.mc_out) + off, v[u]);
         }
       }
       continue;
@@ -479,8 +452,8 @@ __device__ __forceinline__ void reduce_cta(const OpParams& p, uint32_t smem_base
       const long long off = base + chunk_off(i);
       ptx::mbar_expect_tx(bar(BAR_SLOT + slot), len * W);
       for (int src = 0; src < W; ++src)
-        ptx::bulk_g2s(smem_base + slot * set_bytes + src * kReduceChunk,
-                      static_cast<const char*>(p.peer_data[src]) + off, len, bar(BAR_SLOT + slot));
+        ptx::bulk_g2s(smem_base + slot * set_bytes + src * kReduceChunk, src_base(src) + off, len,
+                      bar(BAR_SLOT + slot));
     };
     if (tid == 0)
       for (int i = 0; i < n_mine && i < ns; ++i) issue(i, pos + i);
@@ -502,7 +475,7 @@ __device__ __forceinline__ void reduce_cta(const OpParams& p, uint32_t smem_base
         v.w = ptx::pack_bf16x2(acc[6], acc[7]);
         const long long off = base + chunk_off(i) + tid * 16;
         if (OP == OP_RS) {
-          ptx::st_global_v4(static_cast<char*>(p.peer_data[s.rank]) + off, v);
+          ptx::st_global_v4(local + off, v);
         } else {
           for (int dst = 0; dst < W; ++dst)
             ptx::st_global_v4(static_cast<char*>(p.peer_out[dst]) + off, v);
@@ -577,7 +550,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
   const uint32_t epoch = *s_epoch;
 
   if (is_comm) {
-    if (OP == OP_AG) gather_cta(p, smem_base, bar_base, wc, epoch, ring_bytes);
+    if (OP == OP_AG) gather_push_cta(p, wc, epoch);
     if (OP == OP_RS || OP == OP_AR) reduce_cta<OP>(p, smem_base, bar_base, wc, epoch, ring_bytes);
   } else {
     compute_cta<OP>(&tma_a, &tma_b, p, smem_base, bar_base, s_tmem, wc, epoch);

@@ -422,14 +422,7 @@ int mk_gemm_ar_launch(const void* A, const void* B, const mk_symm_view* C,
   a.M = M; a.N = N; a.K = K; a.b_layout = b_layout; a.rank = C->rank; a.world = C->world;
   a.sync = barrier; a.data = C; a.out = C_final; a.epoch = epoch;
   a.C = C->peer[C->rank];
-  rc = run_op(a, static_cast<cudaStream_t>(stream));
-  if (rc != MK_OK) return rc;
-  if (C->world == 1) {
-    // One GPU: the partial product is the result.
-    MKB_CUDA(cudaMemcpyAsync(C_final->peer[0], C->peer[0], (size_t)M * N * 2,
-                             cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream)));
-  }
-  return MK_OK;
+  return run_op(a, static_cast<cudaStream_t>(stream));
 }
 
 int mk_op_status(const mk_symm_view* sync, uint32_t out4[4]) {
