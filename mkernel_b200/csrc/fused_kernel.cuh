@@ -304,7 +304,8 @@ __device__ __forceinline__ void compute_cta(const CUtensorMap* tma_a, const CUte
 // serve the same peer at a time.  NVSwitch multicast: one multimem store lands in every replica,
 // so there is a single pass over the shard.  After the stores of a group: CTA barrier, one
 // system-scope fence, then the group's flag is written on the receiving rank(s).
-__device__ __forceinline__ void gather_push_cta(const OpParams& p, WaitCtx& wc, uint32_t epoch) {
+__device__ __forceinline__ void gather_push_cta(const OpParams& p, uint32_t ring, WaitCtx& wc,
+                                                uint32_t epoch) {
   const Sched& s = p.sched;
   const int tid = threadIdx.x;
   const int W = s.world;
@@ -328,20 +329,28 @@ __device__ __forceinline__ void gather_push_cta(const OpParams& p, WaitCtx& wc, 
     const long long base = (static_cast<long long>(rowblock_row0(s, rowblock)) + r0) * row_bytes;
     const int dst_rank = (s.rank - d + W) % W;
     char* dst = nvls ? static_cast<char*>(p.mc_data) : static_cast<char*>(p.peer_data[dst_rank]);
-    const long long stride = static_cast<long long>(kThreads) * 16;
-    for (long long off = static_cast<long long>(tid) * 16; off < bytes; off += 4 * stride) {
-      uint4 v[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u)
-        if (off + u * stride < bytes) v[u] = ptx::ld_global_v4_stream(local + base + off + u * stride);
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        if (off + u * stride < bytes) {
-          if (nvls) ptx::multimem_st_v4(dst + base + off + u * stride, v[u]);
-          else ptx::st_global_v4(dst + base + off + u * stride, v[u]);
-        }
-      }
+    // Per-thread ring of kRingVec 16-byte slots in shared memory filled by cp.async: up to
+    // 39 x 16 B x 256 threads = 156 KB of local reads in flight, then a posted store per slot.
+    const long long n_vec = bytes / 16;
+    const long long n_mine = n_vec > tid ? (n_vec - 1 - tid) / kThreads + 1 : 0;
+    auto vec_off = [&](long long e) { return base + (e * kThreads + tid) * 16; };
+    auto slot = [&](long long e) {
+      return ring + (static_cast<uint32_t>(e % kRingVec) * kThreads + tid) * 16u;
+    };
+    for (long long e = 0; e < kRingVec - 1; ++e) {
+      if (e < n_mine) ptx::cp_async_16(slot(e), local + vec_off(e));
+      ptx::cp_async_commit();
     }
+    for (long long e = 0; e < n_mine; ++e) {
+      const long long nx = e + kRingVec - 1;
+      if (nx < n_mine) ptx::cp_async_16(slot(nx), local + vec_off(nx));
+      ptx::cp_async_commit();
+      ptx::cp_async_wait<kRingVec - 1>();
+      const uint4 v = ptx::ld_shared_v4(slot(e));
+      if (nvls) ptx::multimem_st_v4(dst + vec_off(e), v);
+      else ptx::st_global_v4(dst + vec_off(e), v);
+    }
+    ptx::cp_async_wait<0>();
     __syncthreads();
     if (tid == 0) {
       ptx::fence_acq_rel_sys();
@@ -368,18 +377,96 @@ __device__ __forceinline__ void accumulate_bf16x8(float (&acc)[8], const uint4& 
   }
 }
 
+struct ReduceSpan {
+  const char* src[kMaxWorld];  // W partial copies of the same byte range
+  char* dst[kMaxWorld];        // RS: dst[0] only; AR: every rank's output
+  void* mc_dst;                // AR through NVSwitch multicast (or nullptr)
+  long long n_vec;             // 16-byte vectors in the range
+};
+
+// Sums W copies of a byte range.  Each thread owns one 16-byte vector per chunk of 4 KB and
+// keeps DC-1 chunks (x W copies) in flight in a private shared-memory ring filled by cp.async,
+// so the role is bounded by bandwidth rather than by one memory latency per step, and needs no
+// CTA-wide synchronisation.  fp32 accumulation in fixed rank order 0..W-1.
+template <int OP, int WT>
+__device__ __forceinline__ void reduce_span(const ReduceSpan& sp, int W, int n_comm,
+                                            uint32_t ring) {
+  constexpr int DC = kRingVec / WT;  // ring depth in chunks
+  const int tid = threadIdx.x;
+  const long long n_chunks = (sp.n_vec + kThreads - 1) / kThreads;
+  const long long n_mine = n_chunks > blockIdx.x ? (n_chunks - 1 - blockIdx.x) / n_comm + 1 : 0;
+  auto vec_of = [&](long long i) { return (blockIdx.x + i * n_comm) * kThreads + tid; };
+  auto slot = [&](long long i, int src) {
+    return ring + ((static_cast<uint32_t>(i % DC) * WT + src) * kThreads + tid) * 16u;
+  };
+  auto issue = [&](long long i) {
+    if (i < n_mine) {
+      const long long v = vec_of(i);
+      if (v < sp.n_vec) {
+#pragma unroll
+        for (int src = 0; src < WT; ++src)
+          if (src < W) ptx::cp_async_16(slot(i, src), sp.src[src] + v * 16);
+      }
+    }
+    ptx::cp_async_commit();
+  };
+  for (long long i = 0; i < DC - 1; ++i) issue(i);
+  for (long long i = 0; i < n_mine; ++i) {
+    issue(i + DC - 1);
+    ptx::cp_async_wait<DC - 1>();
+    const long long v = vec_of(i);
+    if (v >= sp.n_vec) continue;
+    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int src = 0; src < WT; ++src)
+      if (src < W) accumulate_bf16x8(acc, ptx::ld_shared_v4(slot(i, src)));
+    uint4 r;
+    r.x = ptx::pack_bf16x2(acc[0], acc[1]);
+    r.y = ptx::pack_bf16x2(acc[2], acc[3]);
+    r.z = ptx::pack_bf16x2(acc[4], acc[5]);
+    r.w = ptx::pack_bf16x2(acc[6], acc[7]);
+    if (OP == OP_RS) {
+      ptx::st_global_v4(sp.dst[0] + v * 16, r);
+    } else if (sp.mc_dst != nullptr) {
+      ptx::multimem_st_v4(static_cast<char*>(sp.mc_dst) + v * 16, r);
+    } else {
+#pragma unroll
+      for (int d = 0; d < WT; ++d)
+        if (d < W) ptx::st_global_v4(sp.dst[d] + v * 16, r);
+    }
+  }
+  ptx::cp_async_wait<0>();
+}
+
+// AllReduce through NVSwitch: one multimem load returns the fp32-accumulated sum of all replicas.
+template <int U>
+__device__ __forceinline__ void reduce_span_nvls(const char* mc_src, char* mc_dst, long long n_vec,
+                                                 int n_comm) {
+  const long long per_chunk = static_cast<long long>(U) * kThreads;
+  const long long n_chunks = (n_vec + per_chunk - 1) / per_chunk;
+  for (long long c = blockIdx.x; c < n_chunks; c += n_comm) {
+    const long long v0 = c * per_chunk + threadIdx.x;
+    uint4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long idx = v0 + static_cast<long long>(u) * kThreads;
+      if (idx < n_vec) v[u] = ptx::multimem_ld_reduce_bf16x8(mc_src + idx * 16);
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const long long idx = v0 + static_cast<long long>(u) * kThreads;
+      if (idx < n_vec) ptx::multimem_st_v4(mc_dst + idx * 16, v[u]);
+    }
+  }
+}
+
 template <int OP>
-__device__ __forceinline__ void reduce_cta(const OpParams& p, uint32_t smem_base,
-                                           uint32_t bar_base, WaitCtx& wc, uint32_t epoch,
-                                           int ring_bytes) {
+__device__ __forceinline__ void reduce_cta(const OpParams& p, uint32_t ring, WaitCtx& wc,
+                                           uint32_t epoch) {
   const Sched& s = p.sched;
   const int tid = threadIdx.x;
   const int W = s.world;
   wc.where = (blockIdx.x << 8) | 9u;
-  auto bar = [&](int slot) { return bar_base + 8u * slot; };
-  const int set_bytes = W * kReduceChunk;
-  int ns = ring_bytes / set_bytes;
-  if (ns > 24) ns = 24;
   const uint32_t* flags = p.sync + SW_FLAGS;
   const int n_items = owner_num_items(s, s.rank);
   const int first_block = owner_first_block(s, s.rank);
@@ -387,12 +474,6 @@ __device__ __forceinline__ void reduce_cta(const OpParams& p, uint32_t smem_base
   // ReduceScatter sums W slabs of its own buffer; AllReduce fetches every rank's partial.
   const bool nvls = OP == OP_AR && p.use_nvls && p.mc_data != nullptr && p.mc_out != nullptr;
   char* const local = static_cast<char*>(p.peer_data[s.rank]);
-  auto src_base = [&](int src) -> const char* {
-    if (OP == OP_RS)
-      return local + (static_cast<long long>(src) - s.rank) * s.part_rows * row_bytes;
-    return static_cast<const char*>(p.peer_data[src]);
-  };
-  long long pos = 0;  // ring position, continues across items
 
   for (int k = 0; k < n_items; ++k) {
     const int rb = first_block + k;
@@ -411,80 +492,33 @@ __device__ __forceinline__ void reduce_cta(const OpParams& p, uint32_t smem_base
     int row0, row1;
     owner_item_rows(s, s.rank, k, &row0, &row1);
     const long long base = static_cast<long long>(row0) * row_bytes;
-    const long long bytes = static_cast<long long>(row1 - row0) * row_bytes;
-    const int n_chunks = static_cast<int>((bytes + kReduceChunk - 1) / kReduceChunk);
-    const int n_mine = n_chunks > static_cast<int>(blockIdx.x)
-                           ? (n_chunks - 1 - static_cast<int>(blockIdx.x)) / p.n_comm + 1 : 0;
-    auto chunk_off = [&](int i) {
-      return static_cast<long long>(blockIdx.x + static_cast<long long>(i) * p.n_comm) * kReduceChunk;
-    };
-    auto chunk_len = [&](int i) {
-      long long nb = bytes - chunk_off(i);
-      return static_cast<uint32_t>(nb > kReduceChunk ? kReduceChunk : nb);
-    };
+    const long long n_vec = static_cast<long long>(row1 - row0) * row_bytes / 16;
 
+    // 2. sum the W copies of the item's rows
     if (nvls) {
-      // 2a. NVSwitch path: one multimem load returns the fp32-accumulated sum of all replicas.
-      for (int i0 = 0; i0 < n_mine; i0 += 4) {
-        uint4 v[4];
-        bool have[4];
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          have[u] = (i0 + u < n_mine) && (static_cast<uint32_t>(tid) * 16u < chunk_len(i0 + u));
-          if (have[u])
-            v[u] = ptx::multimem_ld_reduce_bf16x8(static_cast<const char*>(p.mc_data) + base +
-                                                  chunk_off(i0 + u) + tid * 16);
-        }
-#pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          if (!have[u]) continue;
-          const long long off = base + chunk_off(i0 + u) + tid * 16;
-          ptx::multimem_st_v4(static_cast<char*>(p.mc_out) + off, v[u]);
-        }
-      }
+      reduce_span_nvls<8>(static_cast<const char*>(p.mc_data) + base,
+                          static_cast<char*>(p.mc_out) + base, n_vec, p.n_comm);
       continue;
     }
-
-    // 2b. peer-to-peer path: bulk-copy the W partial chunks into shared memory, sum, store.
-    auto issue = [&](int i, long long at) {
-      const int slot = static_cast<int>(at % ns);
-      const uint32_t len = chunk_len(i);
-      const long long off = base + chunk_off(i);
-      ptx::mbar_expect_tx(bar(BAR_SLOT + slot), len * W);
-      for (int src = 0; src < W; ++src)
-        ptx::bulk_g2s(smem_base + slot * set_bytes + src * kReduceChunk, src_base(src) + off, len,
-                      bar(BAR_SLOT + slot));
-    };
-    if (tid == 0)
-      for (int i = 0; i < n_mine && i < ns; ++i) issue(i, pos + i);
-    for (int i = 0; i < n_mine; ++i, ++pos) {
-      const int slot = static_cast<int>(pos % ns);
-      const uint32_t parity = static_cast<uint32_t>((pos / ns) & 1);
-      bounded_wait<false>(wc, [&] { return ptx::mbar_try_wait(bar(BAR_SLOT + slot), parity); },
-                          ST_TIMEOUT_COPY, rb, i);
-      const uint32_t len = chunk_len(i);
-      if (static_cast<uint32_t>(tid) * 16u < len) {
-        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
-        const uint32_t src0 = smem_base + slot * set_bytes + tid * 16;
-        for (int src = 0; src < W; ++src)
-          accumulate_bf16x8(acc, ptx::ld_shared_v4(src0 + src * kReduceChunk));
-        uint4 v;
-        v.x = ptx::pack_bf16x2(acc[0], acc[1]);
-        v.y = ptx::pack_bf16x2(acc[2], acc[3]);
-        v.z = ptx::pack_bf16x2(acc[4], acc[5]);
-        v.w = ptx::pack_bf16x2(acc[6], acc[7]);
-        const long long off = base + chunk_off(i) + tid * 16;
-        if (OP == OP_RS) {
-          ptx::st_global_v4(local + off, v);
-        } else {
-          for (int dst = 0; dst < W; ++dst)
-            ptx::st_global_v4(static_cast<char*>(p.peer_out[dst]) + off, v);
-        }
+    ReduceSpan sp;
+    sp.n_vec = n_vec;
+    sp.mc_dst = (OP == OP_AR && p.use_nvls && p.mc_out != nullptr)
+                    ? static_cast<char*>(p.mc_out) + base : nullptr;
+    for (int r = 0; r < kMaxWorld; ++r) {
+      if (r < W) {
+        // RS: slab r of this rank's buffer holds rank r's partial of this rank's rows.
+        sp.src[r] = (OP == OP_RS)
+                        ? local + base + (static_cast<long long>(r) - s.rank) * s.part_rows * row_bytes
+                        : static_cast<const char*>(p.peer_data[r]) + base;
+        sp.dst[r] = (OP == OP_RS) ? local + base : static_cast<char*>(p.peer_out[r]) + base;
+      } else {
+        sp.src[r] = nullptr;
+        sp.dst[r] = nullptr;
       }
-      __syncthreads();  // every thread has read the slot
-      if (*wc.s_abort != 0u) return;
-      if (tid == 0 && i + ns < n_mine) issue(i + ns, pos + ns);
     }
+    if (W <= 2) reduce_span<OP, 2>(sp, W, p.n_comm, ring);
+    else if (W <= 4) reduce_span<OP, 4>(sp, W, p.n_comm, ring);
+    else reduce_span<OP, 8>(sp, W, p.n_comm, ring);
   }
 }
 
@@ -550,8 +584,8 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
   const uint32_t epoch = *s_epoch;
 
   if (is_comm) {
-    if (OP == OP_AG) gather_push_cta(p, wc, epoch);
-    if (OP == OP_RS || OP == OP_AR) reduce_cta<OP>(p, smem_base, bar_base, wc, epoch, ring_bytes);
+    if (OP == OP_AG) gather_push_cta(p, smem_base, wc, epoch);
+    if (OP == OP_RS || OP == OP_AR) reduce_cta<OP>(p, smem_base, wc, epoch);
   } else {
     compute_cta<OP>(&tma_a, &tma_b, p, smem_base, bar_base, s_tmem, wc, epoch);
   }

@@ -110,6 +110,19 @@ __device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
   return v;
 }
 
+// Asynchronous 16-byte copy global -> shared (no destination registers, so many can be in flight
+// per thread); completion is tracked per thread with commit/wait groups.
+__device__ __forceinline__ void cp_async_16(uint32_t dst, const void* src) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() {
+  asm volatile("cp.async.commit_group;" ::: "memory");
+}
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
 // NVSwitch multicast ("multimem") accesses on a multicast-mapped address: one 16-byte store lands
 // in every bound GPU's replica; one 16-byte load returns the fp32-accumulated sum of all replicas.
 __device__ __forceinline__ void multimem_st_v4(void* mc, uint4 v) {

@@ -26,8 +26,7 @@ constexpr int kBlockM = 128;
 constexpr int kBlockK = 64;
 constexpr int kThreads = 256;
 constexpr int kGatherSub = 8;          // AllGather: a 128-row block lands as 8 groups of 16 rows
-constexpr int kGatherChunk = 16384;    // bytes per bulk copy in the gather ring
-constexpr int kReduceChunk = 4096;     // bytes per peer per reduce step (256 threads x 16 B)
+constexpr int kRingVec = 40;           // exchange role: 16-byte ring slots per thread (160 KB/CTA)
 constexpr int kMaxStages = 8;
 constexpr int kSmemBudget = 232448;    // 227 KiB opt-in limit per CTA on sm_100
 constexpr int kSmemBarrierBytes = 512;
