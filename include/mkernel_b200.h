@@ -109,6 +109,21 @@ int mk_gemm_rs_prepare(const mk_symm_view* sync, void* stream);
 int mk_gemm_rs_launch(const void* A, const void* B, const mk_symm_view* C,
                       const mk_symm_view* sync, int M, int N, int K, void* stream);
 
+/* One-GPU GEMM + ReduceScatter that allocates nothing: C[M,N] = A[M,K] * B[N,K]^T with the
+ * kernel's synchronisation words held in a 64 KiB device array built into the library, for
+ * callers that cannot allocate device memory where they need the product (a process whose GPU
+ * memory is fully owned by a pre-sized arena, or a path that must not hit cudaMalloc's device
+ * synchronisation).  No counterpart in the reference.  Limits and rules:
+ *  - world size 1 only; the output may have at most 16320 tiles of 128 x block_n
+ *    (e.g. 8192 x 8192 is fine, 32768 x 28672 is rejected with MK_ERR_INVALID);
+ *  - the first call on each device looks up the array's device address; make that call
+ *    before starting any stream capture;
+ *  - all calls on a device share the one array: calls that overlap on the GPU (two streams)
+ *    race; calls on one stream are safe;
+ *  - calls no cudaMalloc/cudaFree; the array stays resident on every GPU that loads the library. */
+int mk_gemm_rs_launch_noalloc(const void* A, const void* B, void* C, int M, int N, int K,
+                              void* stream);
+
 /* GEMM + AllReduce.  Replaces gemm_ar_intranode_blackwell
  * (include/operators/gemm_ar/gemm_ar_blackwell.cuh:205-246, src/gemm_ar_blackwell.cu:57-610).
  * A: [M, K_local], B: [K_local, N] (MK_B_KN) or [N, K_local] (MK_B_NK).  C: symmetric [M, N]

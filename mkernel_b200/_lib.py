@@ -81,6 +81,8 @@ _SIGNATURES = {
     "mk_gemm_rs_prepare": (c_int, [POINTER(SymmView), c_void_p]),
     "mk_gemm_rs_launch": (c_int, [c_void_p, c_void_p, POINTER(SymmView), POINTER(SymmView),
                                   c_int, c_int, c_int, c_void_p]),
+    "mk_gemm_rs_launch_noalloc": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                          c_void_p]),
     "mk_gemm_ar_launch": (c_int, [c_void_p, c_void_p, POINTER(SymmView), POINTER(SymmView),
                                   POINTER(SymmView), c_int, c_int, c_int, c_uint32, c_int,
                                   c_void_p]),

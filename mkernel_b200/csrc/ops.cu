@@ -399,6 +399,70 @@ int mk_gemm_rs_launch(const void* A, const void* B, const mk_symm_view* C,
   return run_op(a, static_cast<cudaStream_t>(stream));
 }
 
+// ---- one-GPU GEMM+ReduceScatter that allocates nothing --------------------------------------
+// The synchronisation words the kernel needs (epoch, CTA counters, status) normally live in a
+// buffer the caller allocates.  Some callers cannot allocate device memory at the point where
+// they need the product: code running inside a pre-planned memory arena that owns every byte of
+// the GPU (an inference server that sized its pools at start-up), or code on a path where
+// cudaMalloc's implicit device synchronisation is not acceptable.  For them the words live in
+// this file-scope device array, which every GPU that loads the library holds until exit.
+// In host code the array's name is only a handle for the runtime, not a device address: the
+// address is looked up once per device with cudaGetSymbolAddress and that pointer is what the
+// kernel receives.
+constexpr int kNoAllocSyncWords = 16384;  // 64 KiB: header (64 words) + one word per output tile
+static __device__ __align__(256) uint32_t g_noalloc_sync_words[kNoAllocSyncWords];
+
+static int noalloc_sync_address(uint32_t** out) {
+  static uint32_t* per_device[64];
+  static std::mutex mu;
+  int dev = 0;
+  MKB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return set_error(MK_ERR_INVALID, "device index %d out of range", dev);
+  std::lock_guard<std::mutex> g(mu);
+  if (per_device[dev] == nullptr) {
+    void* p = nullptr;
+    MKB_CUDA(cudaGetSymbolAddress(&p, g_noalloc_sync_words));
+    if (p == nullptr) return set_error(MK_ERR_CUDA, "cudaGetSymbolAddress returned a null address");
+    per_device[dev] = static_cast<uint32_t*>(p);
+  }
+  *out = per_device[dev];
+  return MK_OK;
+}
+
+int mk_gemm_rs_launch_noalloc(const void* A, const void* B, void* C, int M, int N, int K,
+                              void* stream) {
+  if (!A || !B || !C) return set_error(MK_ERR_INVALID, "mk_gemm_rs_launch_noalloc: null operand");
+  int sms = 0;
+  int rc = device_sm_count(&sms);
+  if (rc != MK_OK) return rc;
+  Plan pl;
+  rc = make_plan(OP_RS, 0, 1, M, N, K, MK_B_NK, sms, &pl);
+  if (rc != MK_OK) return rc;
+  const long long need = sync_words_needed(pl.sched);
+  if (need > kNoAllocSyncWords)
+    return set_error(MK_ERR_INVALID,
+                     "mk_gemm_rs_launch_noalloc: %d x %d output needs %lld synchronisation words, "
+                     "the built-in buffer holds %d (at most %d output tiles); use "
+                     "mk_gemm_rs_launch with a caller-provided buffer",
+                     M, N, need, kNoAllocSyncWords, kNoAllocSyncWords - SW_FLAGS);
+  uint32_t* words = nullptr;
+  rc = noalloc_sync_address(&words);  // first call on a device: looks the address up
+  if (rc != MK_OK) return rc;
+  // The array keeps whatever the previous call left: counters and status must start at zero.
+  MKB_CUDA(cudaMemsetAsync(words, 0, (size_t)SW_FLAGS * 4, static_cast<cudaStream_t>(stream)));
+  mk_symm_view sv, cv;
+  memset(&sv, 0, sizeof(sv));
+  memset(&cv, 0, sizeof(cv));
+  sv.rank = 0; sv.world = 1; sv.bytes = (size_t)kNoAllocSyncWords * 4; sv.peer[0] = words;
+  cv.rank = 0; cv.world = 1; cv.bytes = (size_t)M * N * 2; cv.peer[0] = C;
+  OpArgs a;
+  memset(&a, 0, sizeof(a));
+  a.op = OP_RS; a.A = A; a.a_rows = M; a.B = B; a.C = C;
+  a.M = M; a.N = N; a.K = K; a.b_layout = MK_B_NK; a.rank = 0; a.world = 1;
+  a.sync = &sv; a.data = &cv;
+  return run_op(a, static_cast<cudaStream_t>(stream));
+}
+
 int mk_gemm_ar_launch(const void* A, const void* B, const mk_symm_view* C,
                       const mk_symm_view* barrier, const mk_symm_view* C_final, int M, int N,
                       int K, uint32_t epoch, int b_layout, void* stream) {

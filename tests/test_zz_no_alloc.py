@@ -1,0 +1,66 @@
+"""The entry point that allocates nothing (mk_gemm_rs_launch_noalloc).
+
+It exists for callers that cannot allocate device memory at the point of the call -- for
+example a server whose GPU memory is entirely owned by a pre-sized arena, or a latency-critical
+path that must not run into cudaMalloc's device-wide synchronisation.  The kernel's
+synchronisation words then live in a fixed 64 KiB device array inside the library.  The test
+calls it through the C ABI twice in a row (the array keeps the previous call's contents, so the
+second call proves the per-call clearing) and requires exactly the bytes the regular entry point
+(mk_gemm_rs_launch with a caller-allocated buffer) produces.  Collected last on purpose.
+"""
+import ctypes
+
+import pytest
+import torch
+
+from mkernel_b200 import _lib
+from oracle import tp_gemm_oracle as orc
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def _view(t: torch.Tensor) -> _lib.SymmView:
+    v = _lib.SymmView()
+    v.rank, v.world, v.bytes = 0, 1, t.numel() * t.element_size()
+    v.peer[0] = t.data_ptr()
+    return v
+
+
+def test_noalloc_matches_regular_entry_point_twice():
+    lib = _lib.lib()
+    torch.cuda.set_device(0)
+    M, N, K = 640, 768, 512
+    a, b_kn = orc.synth_inputs("rs", 0, 1, M, N, K, seed=2)
+    A = a.to(DEV)
+    B = b_kn.t().contiguous().to(DEV)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    # regular entry point, caller-allocated synchronisation words
+    C_ref = torch.zeros((M, N), device=DEV, dtype=torch.bfloat16)
+    sync = torch.zeros((_lib.MK_RS_SYNC_WORDS,), device=DEV, dtype=torch.int32)
+    cv, sv = _view(C_ref), _view(sync)
+    _lib.check(lib.mk_gemm_rs_launch(A.data_ptr(), B.data_ptr(), ctypes.byref(cv),
+                                     ctypes.byref(sv), M, N, K, stream))
+    torch.cuda.synchronize()
+    assert orc.rel_error(C_ref.cpu(), orc.gemm_rs_ref([a], [b_kn])[0]) <= orc.REL_TOL
+
+    for call in range(2):
+        C = torch.full((M, N), float("nan"), device=DEV, dtype=torch.bfloat16)
+        before = torch.cuda.memory_allocated()
+        _lib.check(lib.mk_gemm_rs_launch_noalloc(A.data_ptr(), B.data_ptr(), C.data_ptr(),
+                                                 M, N, K, stream))
+        torch.cuda.synchronize()
+        assert torch.cuda.memory_allocated() == before
+        assert torch.equal(C, C_ref), f"call {call}: output differs from the regular entry point"
+
+
+def test_noalloc_rejects_sizes_beyond_its_buffer():
+    lib = _lib.lib()
+    torch.cuda.set_device(0)
+    x = torch.zeros(16, device=DEV, dtype=torch.bfloat16)   # never dereferenced: rejected first
+    rc = lib.mk_gemm_rs_launch_noalloc(x.data_ptr(), x.data_ptr(), x.data_ptr(), 32768, 28672,
+                                       8192, None)
+    assert rc == -1
+    assert "built-in buffer" in _lib.last_error()
+    assert lib.mk_gemm_rs_launch_noalloc(None, None, None, 128, 128, 64, None) == -1
