@@ -102,8 +102,8 @@ int mk_ag_gemm_launch(const mk_symm_view* A, const mk_symm_view* ready, const vo
 
 /* GEMM + ReduceScatter.  Replaces gemm_rs_blackwell_prepare / _launch
  * (src/gemm_rs_blackwell.cu:642-732).  A: [M, K_local], B: [N, K_local], C: symmetric [M, N]
- * (receives the partial product, then rows [rank*M/W, (rank+1)*M/W) are overwritten with the
- * reduced result).  sync: symmetric MK_RS_SYNC_WORDS.  prepare zeroes sync once; the caller
+ * (workspace: rank s's partial rows of owner o land in slab s of o's copy; after the launch rows
+ * [rank*M/W, (rank+1)*M/W) hold the reduced result).  sync: symmetric MK_RS_SYNC_WORDS.  prepare zeroes sync once; the caller
  * then synchronises the stream and barriers all ranks before the first launch. */
 int mk_gemm_rs_prepare(const mk_symm_view* sync, void* stream);
 int mk_gemm_rs_launch(const void* A, const void* B, const mk_symm_view* C,
@@ -140,7 +140,7 @@ int mk_op_status(const mk_symm_view* sync, uint32_t out4[4]);
 int mk_op_status_clear(const mk_symm_view* sync, void* stream);
 
 /* ---- options (process-wide): "wait_limit_ms" (device wait budget, default 4000),
- *      "n_comm" (exchange CTAs, 0 = heuristic), "block_n" (0 = heuristic), "group_rows",
+ *      "n_comm" (dedicated exchange CTAs, -1 = heuristic), "block_n" (0 = heuristic), "group_rows",
  *      "use_nvls" (0/1: reduce through NVSwitch multicast when the buffers have an alias). */
 int mk_set_option(const char* name, long long value);
 long long mk_get_option(const char* name);

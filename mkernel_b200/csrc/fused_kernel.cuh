@@ -1,20 +1,27 @@
 // One persistent sm_100a kernel for the tensor-parallel GEMM + collective operators.
 //
-// CTA roles (fixed for the lifetime of the kernel, chosen by blockIdx.x):
-//   exchange CTAs [0, n_comm)  AllGather: push this rank's A rows into every peer's gathered buffer
-//                              with posted remote stores (or one NVSwitch multicast store) and
-//                              raise one flag per 16-row group on the receiver.
-//                              ReduceScatter: GEMM tiles are stored straight into the owner's
-//                              buffer (slab = producing rank); the owner waits for the flags of
-//                              a row-block, sums its W local slabs (fp32 accumulate, fixed rank
-//                              order) and writes the bf16 result in place.
-//                              AllReduce: as ReduceScatter but partials stay with their producer
-//                              and are fetched by the owner, which then stores the result into
-//                              every rank's output.
-//   compute CTAs  [n_comm, G)  bf16 GEMM tiles of 128 x block_n: warp 0 feeds a shared-memory ring
-//                              with TMA tile loads, warp 1 issues tcgen05.mma into one of two TMEM
-//                              accumulators, warps 4-7 drain the other accumulator (tcgen05.ld ->
-//                              bf16 -> global), warp 2 publishes finished tiles to their owners.
+// Roles inside a compute CTA (256 threads):
+//   warp 0      TMA producer: fills a shared-memory ring of (A 128x64, B block_n x 64) stages.
+//   warp 1      one thread issues tcgen05.mma into one of two TMEM accumulators.
+//   warp 2      tile publisher (RS/AR): after a tile is in memory, fence and raise its flag on
+//               every owner.
+//   warp 3      exchange worker: pulls exchange work items from a per-rank queue while the GEMM
+//               runs (see below).  Its loads/stores use the LSU, which the MMA pipeline does not.
+//   warps 4-7   epilogue: tcgen05.ld -> bf16 -> transpose through shared memory -> 128-byte row
+//               segments to global memory (local, or the owner GPU for ReduceScatter).
+// CTAs [0, n_comm) are dedicated exchange CTAs: all 8 warps are exchange workers (used when the
+// GEMM cannot fill the machine anyway, e.g. the decode-shaped AllReduce).
+//
+// Exchange work items (handed out in order by an atomic counter, so early items meet early data):
+//   AllGather      push one 16-row group of the own A shard into a peer's gathered buffer with
+//                  posted remote stores (or into all peers with one NVSwitch multicast store),
+//                  then fence and raise the group's flag on the receiver.
+//   ReduceScatter  GEMM tiles were stored straight into the owner's buffer (slab = producing
+//                  rank); an item sums one chunk of the W local slabs (fp32, fixed rank order)
+//                  in place once the row-block's flags are all up.
+//   AllReduce      partials stay with their producer; an item fetches one chunk from all W ranks,
+//                  sums it and stores the result into every rank's output.
+// A worker keeps 12-20 KB of reads in flight in a private shared-memory ring filled by cp.async.
 //
 // Every wait is bounded: when a wait expires the CTA records {code, where, detail} in the status
 // words, raises an abort flag that all other waits observe, and the kernel drains and returns.
@@ -35,7 +42,6 @@ enum BarSlot : int {
   BAR_TFULL = 16,    // [16,18) accumulator ready for the epilogue
   BAR_TEMPTY = 18,   // [18,20) accumulator drained
   BAR_STORED = 20,   // [20,22) tile written to global memory by all four epilogue warps
-  BAR_SLOT = 0,      // [0,24)  ring slot filled                      (exchange CTAs)
   BAR_COUNT = 32,
 };
 
@@ -116,14 +122,30 @@ __device__ __forceinline__ TileInfo tile_info(const Sched& s, int t) {
   return ti;
 }
 
+// Where row `grow` of this rank's GEMM output lives.
+template <int OP>
+__device__ __forceinline__ __nv_bfloat16* output_row(const OpParams& p, int grow) {
+  const Sched& s = p.sched;
+  if (OP == OP_RS && s.world > 1) {
+    // ReduceScatter: the row belongs to owner o and goes straight into o's buffer, into the
+    // slab reserved for this (producing) rank.  Remote when o != rank: posted NVLink writes.
+    int o = grow / s.part_rows;
+    if (o > s.world - 1) o = s.world - 1;
+    const int i = grow - o * s.part_rows;
+    return static_cast<__nv_bfloat16*>(p.peer_data[o]) +
+           static_cast<long long>(s.rank * s.part_rows + i) * p.ldc;
+  }
+  return static_cast<__nv_bfloat16*>(p.C) + static_cast<long long>(grow) * p.ldc;
+}
+
 // ------------------------------------------------------------------------------------------
-// Compute CTA
+// GEMM roles of a compute CTA (warps 0, 1, 2, 4-7)
 // ------------------------------------------------------------------------------------------
 template <int OP>
-__device__ __forceinline__ void compute_cta(const CUtensorMap* tma_a, const CUtensorMap* tma_b,
-                                            const OpParams& p, uint32_t smem_base,
-                                            uint32_t bar_base, volatile uint32_t* s_tmem,
-                                            WaitCtx& wc, uint32_t epoch) {
+__device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CUtensorMap* tma_b,
+                                              const OpParams& p, uint32_t smem_base,
+                                              uint32_t bar_base, uint32_t epi_stage,
+                                              uint32_t tmem_base, WaitCtx& wc, uint32_t epoch) {
   const Sched& s = p.sched;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int cta = blockIdx.x - p.n_comm;
@@ -131,7 +153,6 @@ __device__ __forceinline__ void compute_cta(const CUtensorMap* tma_a, const CUte
   const int total = s.P * s.Q;
   const int bn = s.block_n;
   const int stage_sz = stage_bytes(bn);
-  const uint32_t tmem_base = *s_tmem;
   auto bar = [&](int slot) { return bar_base + 8u * slot; };
   constexpr bool kSignals = (OP == OP_RS || OP == OP_AR);
 
@@ -144,7 +165,7 @@ __device__ __forceinline__ void compute_cta(const CUtensorMap* tma_a, const CUte
     for (int t = cta; t < total && ok; t += n_comp) {
       const TileInfo ti = tile_info(s, t);
       if (OP == OP_AG && s.world > 1 && rowblock_shard(s, ti.rowblock) != s.rank) {
-        // Rows of a remote shard: wait until the exchange CTAs have landed all 16-row groups.
+        // Rows of a remote shard: wait until the sender has landed all 16-row groups here.
         bool mine = true;
         if (lane < kGatherSub) {
           const uint32_t* f = p.sync + SW_FLAGS + gather_flag_index(ti.rowblock, lane);
@@ -221,8 +242,8 @@ __device__ __forceinline__ void compute_cta(const CUtensorMap* tma_a, const CUte
       for (int t = cta; t < total; t += n_comp) {
         const TileInfo ti = tile_info(s, t);
         if (!wait_mbar(wc, bar(BAR_STORED + acc), acc_phase, 0x400u + acc)) break;
-        // The tile's rows are in this GPU's memory; make them visible system-wide, then tell
-        // every owner whose rows intersect the tile.
+        // The tile's rows have been stored (possibly to other GPUs); make them visible
+        // system-wide, then tell every owner whose rows intersect the tile.
         ptx::fence_acq_rel_sys();
         int lo, hi;
         rowblock_owners(s, ti.rowblock, &lo, &hi);
@@ -234,52 +255,65 @@ __device__ __forceinline__ void compute_cta(const CUtensorMap* tma_a, const CUte
       }
     }
   } else if (warp >= 4) {
-    // ---------------- epilogue: TMEM -> registers -> bf16 -> global ----------------
+    // ---------------- epilogue ----------------
+    // TMEM lane = output row, so a thread holds one row of 64 consecutive columns (128 B).
+    // The warp transposes through a private 4 KB shared-memory buffer (16-byte pieces, XOR
+    // swizzled) so that every store instruction writes four complete 128-byte row segments.
     wc.where = (blockIdx.x << 8) | 4u;
     const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter+32) belong to this warp
+    const uint32_t stage_buf = epi_stage + quarter * 4096;
     int acc = 0;
     uint32_t acc_phase = 0;
-    __nv_bfloat16* C = static_cast<__nv_bfloat16*>(p.C);
+    const int sub_row = lane >> 3, piece = lane & 7;
     for (int t = cta; t < total; t += n_comp) {
       const TileInfo ti = tile_info(s, t);
       if (!wait_mbar(wc, bar(BAR_TFULL + acc), acc_phase, 0x500u + acc)) break;
       ptx::tc_fence_after();
-      const int r_in_tile = quarter * 32 + lane;
-      const bool row_ok = r_in_tile < ti.rows;
-      __nv_bfloat16* crow = C + static_cast<long long>(ti.row0 + r_in_tile) * p.ldc;
-      __nv_bfloat16* crow2 = nullptr;  // second destination (AllReduce on one GPU: C_final)
-      if (OP == OP_RS && s.world > 1 && row_ok) {
-        // ReduceScatter: the row belongs to owner o; store it straight into o's buffer, in the
-        // slab reserved for this (producing) rank.  Remote when o != rank: a posted NVLink write.
-        const int grow = ti.row0 + r_in_tile;
-        const int o = grow / s.part_rows;
-        const int i = grow - o * s.part_rows;
-        crow = static_cast<__nv_bfloat16*>(p.peer_data[o]) +
-               static_cast<long long>(s.rank * s.part_rows + i) * p.ldc;
-      }
-      if (OP == OP_AR && s.world == 1)
-        crow2 = static_cast<__nv_bfloat16*>(p.peer_out[0]) +
-                static_cast<long long>(ti.row0 + r_in_tile) * p.ldc;
       const uint32_t t_base = tmem_base + acc * 256 + (static_cast<uint32_t>(quarter * 32) << 16);
-      for (int c = 0; c < bn; c += 32) {
-        uint32_t r[32];
-        ptx::tmem_ld_32x32(t_base + c, r);
+      for (int c = 0; c < bn; c += 64) {
+        const bool two = c + 32 < bn;
+        uint32_t r0[32], r1[32];
+        ptx::tmem_ld_32x32(t_base + c, r0);
+        if (two) ptx::tmem_ld_32x32(t_base + c + 32, r1);
         ptx::tmem_ld_wait();
-        const int col = ti.n0 + c;
-        if (row_ok) {
+        const uint32_t my_row = stage_buf + lane * 128;
 #pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            if (col + g * 8 + 8 <= s.N) {
-              uint4 v;
-              v.x = ptx::pack_bf16x2(__uint_as_float(r[g * 8 + 0]), __uint_as_float(r[g * 8 + 1]));
-              v.y = ptx::pack_bf16x2(__uint_as_float(r[g * 8 + 2]), __uint_as_float(r[g * 8 + 3]));
-              v.z = ptx::pack_bf16x2(__uint_as_float(r[g * 8 + 4]), __uint_as_float(r[g * 8 + 5]));
-              v.w = ptx::pack_bf16x2(__uint_as_float(r[g * 8 + 6]), __uint_as_float(r[g * 8 + 7]));
-              ptx::st_global_v4(crow + col + g * 8, v);
-              if (OP == OP_AR && crow2 != nullptr) ptx::st_global_v4(crow2 + col + g * 8, v);
-            }
+        for (int j = 0; j < 4; ++j) {
+          uint4 v;
+          v.x = ptx::pack_bf16x2(__uint_as_float(r0[j * 8 + 0]), __uint_as_float(r0[j * 8 + 1]));
+          v.y = ptx::pack_bf16x2(__uint_as_float(r0[j * 8 + 2]), __uint_as_float(r0[j * 8 + 3]));
+          v.z = ptx::pack_bf16x2(__uint_as_float(r0[j * 8 + 4]), __uint_as_float(r0[j * 8 + 5]));
+          v.w = ptx::pack_bf16x2(__uint_as_float(r0[j * 8 + 6]), __uint_as_float(r0[j * 8 + 7]));
+          ptx::st_shared_v4(my_row + ((j ^ (lane & 7)) << 4), v);
+        }
+        if (two) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 v;
+            v.x = ptx::pack_bf16x2(__uint_as_float(r1[j * 8 + 0]), __uint_as_float(r1[j * 8 + 1]));
+            v.y = ptx::pack_bf16x2(__uint_as_float(r1[j * 8 + 2]), __uint_as_float(r1[j * 8 + 3]));
+            v.z = ptx::pack_bf16x2(__uint_as_float(r1[j * 8 + 4]), __uint_as_float(r1[j * 8 + 5]));
+            v.w = ptx::pack_bf16x2(__uint_as_float(r1[j * 8 + 6]), __uint_as_float(r1[j * 8 + 7]));
+            ptx::st_shared_v4(my_row + (((j + 4) ^ (lane & 7)) << 4), v);
           }
         }
+        __syncwarp();
+        const int col = ti.n0 + c + piece * 8;
+        const bool col_ok = (piece < (two ? 8 : 4)) && (col + 8 <= s.N);
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          const int r = it * 4 + sub_row;            // row inside this warp's 32 rows
+          const int r_in_tile = quarter * 32 + r;
+          if (col_ok && r_in_tile < ti.rows) {
+            const uint4 v = ptx::ld_shared_v4(stage_buf + r * 128 + ((piece ^ (r & 7)) << 4));
+            const int grow = ti.row0 + r_in_tile;
+            ptx::st_global_v4(output_row<OP>(p, grow) + col, v);
+            if (OP == OP_AR && s.world == 1)   // one GPU: the partial product is the result
+              ptx::st_global_v4(static_cast<__nv_bfloat16*>(p.peer_out[0]) +
+                                    static_cast<long long>(grow) * p.ldc + col, v);
+          }
+        }
+        __syncwarp();
       }
       ptx::tc_fence_before();
       __syncwarp();
@@ -294,79 +328,7 @@ __device__ __forceinline__ void compute_cta(const CUtensorMap* tma_a, const CUte
 }
 
 // ------------------------------------------------------------------------------------------
-// Exchange CTA: AllGather push
-// ------------------------------------------------------------------------------------------
-// Every rank writes its own shard into the gathered buffer of every peer with posted remote
-// stores (a pull would pay one NVLink round trip per request and is latency-bound per SM).
-// Work items are 16-row groups of the own shard.  Peer-to-peer: items are ordered peer-major,
-// nearest deadline first -- rank r's shard is needed first by rank r-1 (ring distance 1 from its
-// point of view), then r-2, ... -- and dealt round-robin to the exchange CTAs so that all of them
-// serve the same peer at a time.  NVSwitch multicast: one multimem store lands in every replica,
-// so there is a single pass over the shard.  After the stores of a group: CTA barrier, one
-// system-scope fence, then the group's flag is written on the receiving rank(s).
-__device__ __forceinline__ void gather_push_cta(const OpParams& p, uint32_t ring, WaitCtx& wc,
-                                                uint32_t epoch) {
-  const Sched& s = p.sched;
-  const int tid = threadIdx.x;
-  const int W = s.world;
-  wc.where = (blockIdx.x << 8) | 8u;
-  const bool nvls = p.use_nvls && p.mc_data != nullptr;
-  const int groups = s.part_blocks * kGatherSub;          // 16-row groups in one shard
-  const int n_items = nvls ? groups : (W - 1) * groups;
-  const char* local = static_cast<const char*>(p.peer_data[s.rank]);
-  const long long row_bytes = static_cast<long long>(p.K) * 2;
-
-  for (int x = blockIdx.x; x < n_items; x += p.n_comm) {
-    const int d = nvls ? 0 : 1 + x / groups;               // ring distance of the receiving rank
-    const int jg = x % groups;
-    const int j = jg / kGatherSub, g = jg % kGatherSub;
-    const int rowblock = s.rank * s.part_blocks + j;
-    const int rows_in_block = rowblock_rows(s, rowblock);
-    const int r0 = g * (kBlockM / kGatherSub);
-    int r1 = r0 + kBlockM / kGatherSub;
-    if (r1 > rows_in_block) r1 = rows_in_block;
-    const long long bytes = r1 > r0 ? (r1 - r0) * row_bytes : 0;
-    const long long base = (static_cast<long long>(rowblock_row0(s, rowblock)) + r0) * row_bytes;
-    const int dst_rank = (s.rank - d + W) % W;
-    char* dst = nvls ? static_cast<char*>(p.mc_data) : static_cast<char*>(p.peer_data[dst_rank]);
-    // Per-thread ring of kRingVec 16-byte slots in shared memory filled by cp.async: up to
-    // 39 x 16 B x 256 threads = 156 KB of local reads in flight, then a posted store per slot.
-    const long long n_vec = bytes / 16;
-    const long long n_mine = n_vec > tid ? (n_vec - 1 - tid) / kThreads + 1 : 0;
-    auto vec_off = [&](long long e) { return base + (e * kThreads + tid) * 16; };
-    auto slot = [&](long long e) {
-      return ring + (static_cast<uint32_t>(e % kRingVec) * kThreads + tid) * 16u;
-    };
-    for (long long e = 0; e < kRingVec - 1; ++e) {
-      if (e < n_mine) ptx::cp_async_16(slot(e), local + vec_off(e));
-      ptx::cp_async_commit();
-    }
-    for (long long e = 0; e < n_mine; ++e) {
-      const long long nx = e + kRingVec - 1;
-      if (nx < n_mine) ptx::cp_async_16(slot(nx), local + vec_off(nx));
-      ptx::cp_async_commit();
-      ptx::cp_async_wait<kRingVec - 1>();
-      const uint4 v = ptx::ld_shared_v4(slot(e));
-      if (nvls) ptx::multimem_st_v4(dst + vec_off(e), v);
-      else ptx::st_global_v4(dst + vec_off(e), v);
-    }
-    ptx::cp_async_wait<0>();
-    __syncthreads();
-    if (tid == 0) {
-      ptx::fence_acq_rel_sys();
-      const long long idx = SW_FLAGS + gather_flag_index(rowblock, g);
-      if (nvls) {
-        for (int r = 0; r < W; ++r)
-          if (r != s.rank) ptx::st_relaxed_sys(p.peer_sync[r] + idx, epoch);
-      } else {
-        ptx::st_relaxed_sys(p.peer_sync[dst_rank] + idx, epoch);
-      }
-    }
-  }
-}
-
-// ------------------------------------------------------------------------------------------
-// Exchange CTA: reduce (ReduceScatter / AllReduce)
+// Exchange workers (one warp each)
 // ------------------------------------------------------------------------------------------
 __device__ __forceinline__ void accumulate_bf16x8(float (&acc)[8], const uint4& v) {
   const uint32_t w[4] = {v.x, v.y, v.z, v.w};
@@ -377,36 +339,53 @@ __device__ __forceinline__ void accumulate_bf16x8(float (&acc)[8], const uint4& 
   }
 }
 
+// AllGather item: copy `n_vec` 16-byte vectors from the own shard to the same offset of the
+// destination (a peer's buffer or the multicast alias) through the lane-private ring.
+template <int R>
+__device__ __forceinline__ void push_span(const char* src, char* dst, long long n_vec, bool nvls,
+                                          uint32_t ring, int lane) {
+  const long long n_mine = n_vec > lane ? (n_vec - 1 - lane) / 32 + 1 : 0;
+  auto off = [&](long long e) { return (e * 32 + lane) * 16; };
+  auto slot = [&](long long e) { return ring + (static_cast<uint32_t>(e % R) * 32u + lane) * 16u; };
+  for (long long e = 0; e < R - 1; ++e) {
+    if (e < n_mine) ptx::cp_async_16(slot(e), src + off(e));
+    ptx::cp_async_commit();
+  }
+  for (long long e = 0; e < n_mine; ++e) {
+    const long long nx = e + R - 1;
+    if (nx < n_mine) ptx::cp_async_16(slot(nx), src + off(nx));
+    ptx::cp_async_commit();
+    ptx::cp_async_wait<R - 1>();
+    const uint4 v = ptx::ld_shared_v4(slot(e));
+    if (nvls) ptx::multimem_st_v4(dst + off(e), v);
+    else ptx::st_global_v4(dst + off(e), v);
+  }
+  ptx::cp_async_wait<0>();
+}
+
 struct ReduceSpan {
-  const char* src[kMaxWorld];  // W partial copies of the same byte range
+  const char* src[kMaxWorld];  // W copies of the same byte range
   char* dst[kMaxWorld];        // RS: dst[0] only; AR: every rank's output
-  void* mc_dst;                // AR through NVSwitch multicast (or nullptr)
+  char* mc_dst;                // AR through NVSwitch multicast (or nullptr)
   long long n_vec;             // 16-byte vectors in the range
 };
 
-// Sums W copies of a byte range.  Each thread owns one 16-byte vector per chunk of 4 KB and
-// keeps DC-1 chunks (x W copies) in flight in a private shared-memory ring filled by cp.async,
-// so the role is bounded by bandwidth rather than by one memory latency per step, and needs no
-// CTA-wide synchronisation.  fp32 accumulation in fixed rank order 0..W-1.
-template <int OP, int WT>
-__device__ __forceinline__ void reduce_span(const ReduceSpan& sp, int W, int n_comm,
-                                            uint32_t ring) {
-  constexpr int DC = kRingVec / WT;  // ring depth in chunks
-  const int tid = threadIdx.x;
-  const long long n_chunks = (sp.n_vec + kThreads - 1) / kThreads;
-  const long long n_mine = n_chunks > blockIdx.x ? (n_chunks - 1 - blockIdx.x) / n_comm + 1 : 0;
-  auto vec_of = [&](long long i) { return (blockIdx.x + i * n_comm) * kThreads + tid; };
+// Reduce item: sum W copies of a range.  Each lane owns every 32nd vector and keeps DC-1 steps
+// (x W copies) of cp.async reads in flight.  fp32 accumulation in fixed rank order 0..W-1.
+template <int OP, int WT, int R>
+__device__ __forceinline__ void reduce_span(const ReduceSpan& sp, int W, uint32_t ring, int lane) {
+  constexpr int DC = R / WT;
+  const long long n_mine = sp.n_vec > lane ? (sp.n_vec - 1 - lane) / 32 + 1 : 0;
+  auto vec_of = [&](long long i) { return i * 32 + lane; };
   auto slot = [&](long long i, int src) {
-    return ring + ((static_cast<uint32_t>(i % DC) * WT + src) * kThreads + tid) * 16u;
+    return ring + ((static_cast<uint32_t>(i % DC) * WT + src) * 32u + lane) * 16u;
   };
   auto issue = [&](long long i) {
     if (i < n_mine) {
       const long long v = vec_of(i);
-      if (v < sp.n_vec) {
 #pragma unroll
-        for (int src = 0; src < WT; ++src)
-          if (src < W) ptx::cp_async_16(slot(i, src), sp.src[src] + v * 16);
-      }
+      for (int src = 0; src < WT; ++src)
+        if (src < W) ptx::cp_async_16(slot(i, src), sp.src[src] + v * 16);
     }
     ptx::cp_async_commit();
   };
@@ -415,7 +394,6 @@ __device__ __forceinline__ void reduce_span(const ReduceSpan& sp, int W, int n_c
     issue(i + DC - 1);
     ptx::cp_async_wait<DC - 1>();
     const long long v = vec_of(i);
-    if (v >= sp.n_vec) continue;
     float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int src = 0; src < WT; ++src)
@@ -428,7 +406,7 @@ __device__ __forceinline__ void reduce_span(const ReduceSpan& sp, int W, int n_c
     if (OP == OP_RS) {
       ptx::st_global_v4(sp.dst[0] + v * 16, r);
     } else if (sp.mc_dst != nullptr) {
-      ptx::multimem_st_v4(static_cast<char*>(sp.mc_dst) + v * 16, r);
+      ptx::multimem_st_v4(sp.mc_dst + v * 16, r);
     } else {
 #pragma unroll
       for (int d = 0; d < WT; ++d)
@@ -439,86 +417,131 @@ __device__ __forceinline__ void reduce_span(const ReduceSpan& sp, int W, int n_c
 }
 
 // AllReduce through NVSwitch: one multimem load returns the fp32-accumulated sum of all replicas.
-template <int U>
 __device__ __forceinline__ void reduce_span_nvls(const char* mc_src, char* mc_dst, long long n_vec,
-                                                 int n_comm) {
-  const long long per_chunk = static_cast<long long>(U) * kThreads;
-  const long long n_chunks = (n_vec + per_chunk - 1) / per_chunk;
-  for (long long c = blockIdx.x; c < n_chunks; c += n_comm) {
-    const long long v0 = c * per_chunk + threadIdx.x;
-    uint4 v[U];
+                                                 int lane) {
+  for (long long v0 = lane; v0 < n_vec; v0 += 32 * 8) {
+    uint4 v[8];
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const long long idx = v0 + static_cast<long long>(u) * kThreads;
-      if (idx < n_vec) v[u] = ptx::multimem_ld_reduce_bf16x8(mc_src + idx * 16);
-    }
+    for (int u = 0; u < 8; ++u)
+      if (v0 + u * 32 < n_vec) v[u] = ptx::multimem_ld_reduce_bf16x8(mc_src + (v0 + u * 32) * 16);
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const long long idx = v0 + static_cast<long long>(u) * kThreads;
-      if (idx < n_vec) ptx::multimem_st_v4(mc_dst + idx * 16, v[u]);
-    }
+    for (int u = 0; u < 8; ++u)
+      if (v0 + u * 32 < n_vec) ptx::multimem_st_v4(mc_dst + (v0 + u * 32) * 16, v[u]);
   }
 }
 
-template <int OP>
-__device__ __forceinline__ void reduce_cta(const OpParams& p, uint32_t ring, WaitCtx& wc,
-                                           uint32_t epoch) {
+// One exchange worker (a full warp).  Pulls items until the queue is empty.  Returns when done
+// or when a wait expired.  `s_item` is a shared-memory word private to this warp.
+template <int OP, int R>
+__device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring, WaitCtx& wc,
+                                                uint32_t epoch, volatile uint32_t* s_item) {
   const Sched& s = p.sched;
-  const int tid = threadIdx.x;
+  const int lane = threadIdx.x & 31;
   const int W = s.world;
-  wc.where = (blockIdx.x << 8) | 9u;
-  const uint32_t* flags = p.sync + SW_FLAGS;
-  const int n_items = owner_num_items(s, s.rank);
-  const int first_block = owner_first_block(s, s.rank);
-  const long long row_bytes = static_cast<long long>(s.N) * 2;
-  // ReduceScatter sums W slabs of its own buffer; AllReduce fetches every rank's partial.
-  const bool nvls = OP == OP_AR && p.use_nvls && p.mc_data != nullptr && p.mc_out != nullptr;
+  if (W <= 1 || p.n_items <= 0) return;
+  wc.where = (blockIdx.x << 8) | 0x10u | (threadIdx.x >> 5);
+  const bool nvls_ag = OP == OP_AG && p.use_nvls && p.mc_data != nullptr;
+  const bool nvls_ar = OP == OP_AR && p.use_nvls && p.mc_data != nullptr && p.mc_out != nullptr;
+  const long long row_bytes = (OP == OP_AG ? static_cast<long long>(p.K) : static_cast<long long>(s.N)) * 2;
   char* const local = static_cast<char*>(p.peer_data[s.rank]);
 
-  for (int k = 0; k < n_items; ++k) {
-    const int rb = first_block + k;
-    // 1. every rank must have published every column block of this row-block
-    {
-      bool ok = true;
-      for (int idx = tid; idx < W * s.Q && ok; idx += kThreads) {
-        const int src = idx / s.Q, q = idx % s.Q;
-        const uint32_t* f = flags + tile_flag_index(s, src, rb, q);
-        ok = bounded_wait<true>(wc, [&] { return ptx::ld_acquire_sys(f) == epoch; },
-                                ST_TIMEOUT_TILE, (src << 24) | rb, q);
-      }
-      __syncthreads();
-      if (*wc.s_abort != 0u) return;
-    }
-    int row0, row1;
-    owner_item_rows(s, s.rank, k, &row0, &row1);
-    const long long base = static_cast<long long>(row0) * row_bytes;
-    const long long n_vec = static_cast<long long>(row1 - row0) * row_bytes / 16;
+  while (true) {
+    if (lane == 0) *s_item = atomicAdd(p.sync + SW_NEXT_ITEM, 1u);
+    __syncwarp();
+    const int item = static_cast<int>(*s_item);
+    __syncwarp();
+    if (item >= p.n_items) break;
 
-    // 2. sum the W copies of the item's rows
-    if (nvls) {
-      reduce_span_nvls<8>(static_cast<const char*>(p.mc_data) + base,
-                          static_cast<char*>(p.mc_out) + base, n_vec, p.n_comm);
-      continue;
+    if (OP == OP_AG) {
+      const int groups = s.part_blocks * kGatherSub;
+      const int d = nvls_ag ? 0 : 1 + item / groups;       // ring distance of the receiver
+      const int jg = item % groups;
+      const int j = jg / kGatherSub, g = jg % kGatherSub;
+      const int rowblock = s.rank * s.part_blocks + j;
+      const int rows_in_block = rowblock_rows(s, rowblock);
+      const int r0 = g * (kBlockM / kGatherSub);
+      int r1 = r0 + kBlockM / kGatherSub;
+      if (r1 > rows_in_block) r1 = rows_in_block;
+      const long long n_vec = r1 > r0 ? (r1 - r0) * row_bytes / 16 : 0;
+      const long long base = (static_cast<long long>(rowblock_row0(s, rowblock)) + r0) * row_bytes;
+      const int dst_rank = (s.rank - d + W) % W;
+      char* dst = nvls_ag ? static_cast<char*>(p.mc_data) : static_cast<char*>(p.peer_data[dst_rank]);
+      push_span<R>(local + base, dst + base, n_vec, nvls_ag, ring, lane);
+      __syncwarp();
+      if (lane == 0) {
+        ptx::fence_acq_rel_sys();
+        const long long idx = SW_FLAGS + gather_flag_index(rowblock, g);
+        if (nvls_ag) {
+          for (int r = 0; r < W; ++r)
+            if (r != s.rank) ptx::st_relaxed_sys(p.peer_sync[r] + idx, epoch);
+        } else {
+          ptx::st_relaxed_sys(p.peer_sync[dst_rank] + idx, epoch);
+        }
+      }
+    } else {
+      const int cpb = reduce_chunks_per_piece(s, p.item_vecs);
+      const int k = item / cpb, c = item % cpb;
+      const int rb = owner_first_block(s, s.rank) + k;
+      // 1. the row-block is complete once every rank has published every column block of it
+      uint32_t* summary = p.sync + SW_FLAGS + summary_flag_index(s, rb);
+      bool ready = ptx::ld_acquire_gpu(summary) == epoch;
+      ready = __shfl_sync(0xffffffffu, ready, 0);
+      if (!ready) {
+        bool ok = true;
+        for (int idx = lane; idx < W * s.Q && ok; idx += 32) {
+          const int src = idx / s.Q, q = idx % s.Q;
+          const uint32_t* f = p.sync + SW_FLAGS + tile_flag_index(s, src, rb, q);
+          ok = bounded_wait<true>(wc, [&] { return ptx::ld_acquire_sys(f) == epoch; },
+                                  ST_TIMEOUT_TILE, (src << 24) | rb, q);
+        }
+        if (!__all_sync(0xffffffffu, ok)) return;
+        if (lane == 0) ptx::st_release_gpu(summary, epoch);
+      }
+      // 2. sum this chunk of the piece
+      int row0, row1;
+      owner_item_rows(s, s.rank, k, &row0, &row1);
+      const long long piece_vecs = static_cast<long long>(row1 - row0) * row_bytes / 16;
+      const long long v_begin = static_cast<long long>(c) * p.item_vecs;
+      long long n_vec = piece_vecs - v_begin;
+      if (n_vec > p.item_vecs) n_vec = p.item_vecs;
+      if (n_vec > 0) {
+        const long long base = static_cast<long long>(row0) * row_bytes + v_begin * 16;
+        if (nvls_ar) {
+          reduce_span_nvls(static_cast<const char*>(p.mc_data) + base,
+                           static_cast<char*>(p.mc_out) + base, n_vec, lane);
+        } else {
+          ReduceSpan sp;
+          sp.n_vec = n_vec;
+          sp.mc_dst = (OP == OP_AR && p.use_nvls && p.mc_out != nullptr)
+                          ? static_cast<char*>(p.mc_out) + base : nullptr;
+#pragma unroll
+          for (int r = 0; r < kMaxWorld; ++r) {
+            // RS: slab r of this rank's buffer holds rank r's partial of this rank's rows.
+            sp.src[r] = r >= W ? nullptr
+                        : (OP == OP_RS)
+                            ? local + base + (static_cast<long long>(r) - s.rank) * s.part_rows * row_bytes
+                            : static_cast<const char*>(p.peer_data[r]) + base;
+            sp.dst[r] = r >= W ? nullptr
+                        : (OP == OP_RS) ? local + base : static_cast<char*>(p.peer_out[r]) + base;
+          }
+          if (W <= 2) reduce_span<OP, 2, R>(sp, W, ring, lane);
+          else if (W <= 4) reduce_span<OP, 4, R>(sp, W, ring, lane);
+          else reduce_span<OP, 8, R>(sp, W, ring, lane);
+        }
+      }
+      __syncwarp();
+      if (lane == 0) ptx::fence_acq_rel_sys();   // results (remote for AR) before "item done"
     }
-    ReduceSpan sp;
-    sp.n_vec = n_vec;
-    sp.mc_dst = (OP == OP_AR && p.use_nvls && p.mc_out != nullptr)
-                    ? static_cast<char*>(p.mc_out) + base : nullptr;
-    for (int r = 0; r < kMaxWorld; ++r) {
-      if (r < W) {
-        // RS: slab r of this rank's buffer holds rank r's partial of this rank's rows.
-        sp.src[r] = (OP == OP_RS)
-                        ? local + base + (static_cast<long long>(r) - s.rank) * s.part_rows * row_bytes
-                        : static_cast<const char*>(p.peer_data[r]) + base;
-        sp.dst[r] = (OP == OP_RS) ? local + base : static_cast<char*>(p.peer_out[r]) + base;
-      } else {
-        sp.src[r] = nullptr;
-        sp.dst[r] = nullptr;
+
+    // 3. the worker that completes the rank's last item tells every rank this rank is done
+    if (lane == 0) {
+      const uint32_t done = atomicAdd(p.sync + SW_ITEMS_DONE, 1u);
+      if (done == static_cast<uint32_t>(p.n_items - 1)) {
+        ptx::fence_acq_rel_sys();
+        for (int r = 0; r < W; ++r) ptx::st_relaxed_sys(p.peer_sync[r] + SW_EXIT + s.rank, epoch);
       }
     }
-    if (W <= 2) reduce_span<OP, 2>(sp, W, p.n_comm, ring);
-    else if (W <= 4) reduce_span<OP, 4>(sp, W, p.n_comm, ring);
-    else reduce_span<OP, 8>(sp, W, p.n_comm, ring);
+    __syncwarp();
   }
 }
 
@@ -536,10 +559,14 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
   const int ring_bytes = p.stages * stage_bytes(s.block_n);
   const uint32_t bar_base = smem_base + ring_bytes;
+  const uint32_t epi_stage = bar_base + kSmemBarrierBytes;
+  const uint32_t xchg_ring = epi_stage + kEpilogueStageBytes;
   uint8_t* gen_base = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
-  volatile uint32_t* s_tmem = reinterpret_cast<volatile uint32_t*>(gen_base + ring_bytes + 8 * BAR_COUNT);
-  volatile uint32_t* s_abort = s_tmem + 1;
-  volatile uint32_t* s_epoch = s_tmem + 2;
+  volatile uint32_t* s_words = reinterpret_cast<volatile uint32_t*>(gen_base + ring_bytes + 8 * BAR_COUNT);
+  volatile uint32_t* s_tmem = s_words;       // TMEM base address
+  volatile uint32_t* s_abort = s_words + 1;  // CTA-wide abort flag
+  volatile uint32_t* s_epoch = s_words + 2;
+  volatile uint32_t* s_item = s_words + 8;   // [8,16): one queue slot per warp
   const bool is_comm = static_cast<int>(blockIdx.x) < p.n_comm;
 
   WaitCtx wc;
@@ -556,9 +583,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
       if (OP == OP_RS) e = ptx::ld_relaxed_sys(p.sync + SW_EPOCH) + 1u;
     }
     *s_epoch = e;
-    if (is_comm) {
-      for (int i = 0; i < 24; ++i) ptx::mbar_init(bar_base + 8u * (BAR_SLOT + i), 1);
-    } else {
+    if (!is_comm) {
       for (int i = 0; i < kMaxStages; ++i) {
         ptx::mbar_init(bar_base + 8u * (BAR_FULL + i), 1);
         ptx::mbar_init(bar_base + 8u * (BAR_EMPTY + i), 1);
@@ -573,6 +598,10 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
       ptx::tma_prefetch_desc(&tma_b);
     }
     ptx::fence_mbar_init();
+    // A rank with nothing to exchange still owes its peers the "finished" signal.
+    if (blockIdx.x == 0 && p.sync != nullptr && s.world > 1 && p.n_items <= 0) {
+      for (int r = 0; r < s.world; ++r) ptx::st_release_sys(p.peer_sync[r] + SW_EXIT + s.rank, e);
+    }
   }
   if (!is_comm && warp == 1) {
     ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(s_tmem)), 512);
@@ -584,10 +613,13 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
   const uint32_t epoch = *s_epoch;
 
   if (is_comm) {
-    if (OP == OP_AG) gather_push_cta(p, smem_base, wc, epoch);
-    if (OP == OP_RS || OP == OP_AR) reduce_cta<OP>(p, smem_base, wc, epoch);
+    if (OP != OP_GEMM)
+      exchange_worker<OP, kRingDedicated>(p, smem_base + warp * (kRingDedicated * 32 * 16), wc,
+                                          epoch, s_item + warp);
+  } else if (warp == 3) {
+    if (OP != OP_GEMM) exchange_worker<OP, kRingInCta>(p, xchg_ring, wc, epoch, s_item + warp);
   } else {
-    compute_cta<OP>(&tma_a, &tma_b, p, smem_base, bar_base, s_tmem, wc, epoch);
+    compute_roles<OP>(&tma_a, &tma_b, p, smem_base, bar_base, epi_stage, *s_tmem, wc, epoch);
   }
 
   // ---------------- teardown ----------------
@@ -608,20 +640,11 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
 
   // ---------------- exit handshake (thread 0 of every CTA) ----------------
   wc.where = (blockIdx.x << 8) | 15u;
-  if (is_comm && s.world > 1) {
-    // The exchange role of this rank is finished once all its exchange CTAs are.
-    ptx::fence_acq_rel_sys();
-    const uint32_t prev = atomicAdd(p.sync + SW_COMM_DONE, 1u);
-    if (prev == static_cast<uint32_t>(p.n_comm - 1)) {
-      ptx::fence_acq_rel_sys();
-      for (int r = 0; r < s.world; ++r) ptx::st_relaxed_sys(p.peer_sync[r] + SW_EXIT + s.rank, epoch);
-    }
-  }
   __threadfence();
   const uint32_t done = atomicAdd(p.sync + SW_GRID_DONE, 1u);
   if (done == gridDim.x - 1) {
-    // Last CTA of this rank: the kernel may only end when every rank has finished reading this
-    // rank's buffers (and, for AllReduce, has written its share of this rank's output).
+    // Last CTA of this rank: the kernel may only end when every rank has finished its exchange
+    // work (nobody still reads or writes this rank's buffers; AllReduce output is complete).
     if (s.world > 1 && *s_abort == 0u) {
       for (int r = 0; r < s.world; ++r) {
         const uint32_t* f = p.sync + SW_EXIT + r;
@@ -631,7 +654,8 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
       }
     }
     p.sync[SW_GRID_DONE] = 0u;
-    p.sync[SW_COMM_DONE] = 0u;
+    p.sync[SW_NEXT_ITEM] = 0u;
+    p.sync[SW_ITEMS_DONE] = 0u;
     if (OP == OP_RS) p.sync[SW_EPOCH] = epoch;
     __threadfence();
   }

@@ -11,7 +11,9 @@ struct OpParams {
   int k_blocks;          // ceil(K / 64)
   int stages;            // operand ring depth
   int b_mn_major;        // 0: B stored [N,K] (K contiguous); 1: B stored [K,N] (N contiguous)
-  int n_comm;            // CTAs [0, n_comm) run the exchange role, the rest run the GEMM
+  int n_comm;            // CTAs [0, n_comm) run only the exchange role, the rest run the GEMM
+  int item_vecs;         // RS/AR: 16-byte vectors per exchange work item
+  int n_items;           // exchange work items of this rank for this launch
   int use_nvls;          // exchange through NVSwitch multicast addresses when available
   uint32_t epoch_arg;    // GEMM+AR: caller-provided epoch; other ops read SW_EPOCH
   uint64_t wait_limit_ns;

@@ -25,7 +25,7 @@ namespace mkb {
 // ------------------------------------------------------------------------------------------
 struct Options {
   long long wait_limit_ms = 4000;
-  long long n_comm = 0;
+  long long n_comm = -1;   // dedicated exchange CTAs; -1 = heuristic
   long long block_n = 0;
   long long group_rows = 0;
   long long use_nvls = 0;
@@ -53,27 +53,17 @@ struct Plan {
 };
 
 static int default_n_comm(int op, int world, int M, int N, int K, int num_sms) {
+  (void)K;
   if (world <= 1 || op == OP_GEMM) return 0;
-  // Small, latency-bound problems cannot fill the machine with tiles even at the narrowest
-  // tile width: give every tile its own CTA and the rest (up to 32) to the exchange role.
+  // Every compute CTA carries one exchange warp, which is enough when the GEMM fills the
+  // machine.  Small, latency-bound problems cannot give every SM a tile even at the narrowest
+  // tile width: the SMs left over (up to 32) become dedicated exchange CTAs with 8 workers each.
   const long long tiles64 = (long long)ceil_div(M, kBlockM) * ceil_div(N, 64);
   if (tiles64 + 2 <= num_sms) {
     int spare = num_sms - (int)tiles64;
     return spare > 32 ? 32 : spare;
   }
-  // Otherwise size the exchange role by the bytes this rank must move in per unit of GEMM time,
-  // assuming ~60 GB/s per exchange CTA (bulk-copy ring, ~180 KB in flight) and the GEMM running
-  // at ~1.2 PFLOP/s.
-  const double flops = 2.0 * M * (double)N * K;
-  double bytes_in;
-  if (op == OP_AG) bytes_in = (double)(world - 1) / world * M * (double)K * 2;
-  else bytes_in = (double)M * N * 2 * (op == OP_AR ? 1.5 : 1.0);  // W copies of a 1/W slice
-  const double t_gemm = flops / 1.2e15;
-  const double need = bytes_in / (t_gemm > 1e-9 ? t_gemm : 1e-9) / 60e9;
-  int n = (int)(need * 1.25 + 0.999);
-  if (n < 2) n = 2;
-  const int cap = num_sms / 5;
-  return n > cap ? cap : n;
+  return 0;
 }
 
 static int make_plan(int op, int rank, int world, int M, int N, int K, int b_layout, int num_sms,
@@ -96,7 +86,7 @@ static int make_plan(int op, int rank, int world, int M, int N, int K, int b_lay
     std::lock_guard<std::mutex> g(g_opt_mu);
     o = g_opt;
   }
-  int n_comm = (int)o.n_comm > 0 && world > 1 && op != OP_GEMM
+  int n_comm = (int)o.n_comm >= 0 && world > 1 && op != OP_GEMM
                    ? (int)o.n_comm : default_n_comm(op, world, M, N, K, num_sms);
   if (n_comm > num_sms - 1) n_comm = num_sms - 1;
   const int n_comp_max = num_sms - n_comm;
@@ -221,8 +211,6 @@ static int run_op(const OpArgs& a, cudaStream_t stream) {
   Plan pl;
   rc = make_plan(a.op, a.rank, a.world, a.M, a.N, a.K, a.b_layout, sms, &pl);
   if (rc != MK_OK) return rc;
-  if (a.world > 1 && pl.n_comm < 1)
-    return set_error(MK_ERR_INVALID, "world > 1 needs at least one exchange CTA");
 
   OpParams p;
   memset(&p, 0, sizeof(p));
@@ -232,6 +220,21 @@ static int run_op(const OpArgs& a, cudaStream_t stream) {
   p.stages = pl.stages;
   p.b_mn_major = pl.b_mn_major;
   p.n_comm = pl.n_comm;
+  bool want_nvls = false;
+  {
+    std::lock_guard<std::mutex> g(g_opt_mu);
+    want_nvls = g_opt.use_nvls != 0;
+  }
+  if (a.world > 1 && a.op != OP_GEMM) {
+    const int workers = (pl.grid - pl.n_comm) + 8 * pl.n_comm;
+    if (a.op == OP_AG) {
+      p.item_vecs = 0;
+      p.n_items = gather_num_items(pl.sched, want_nvls && a.data && a.data->mc != nullptr);
+    } else {
+      p.item_vecs = choose_item_vecs(pl.sched, workers);
+      p.n_items = reduce_num_items(pl.sched, a.rank, p.item_vecs);
+    }
+  }
   p.epoch_arg = a.epoch;
   {
     std::lock_guard<std::mutex> g(g_opt_mu);
@@ -313,7 +316,8 @@ int mk_set_option(const char* name, long long value) {
   std::lock_guard<std::mutex> g(g_opt_mu);
   long long* s = option_slot(name);
   if (!s) return set_error(MK_ERR_INVALID, "unknown option '%s'", name ? name : "(null)");
-  if (value < 0) return set_error(MK_ERR_INVALID, "option '%s' must be >= 0", name);
+  if (value < 0 && !(value == -1 && !strcmp(name, "n_comm")))
+    return set_error(MK_ERR_INVALID, "option '%s' must be >= 0", name);
   *s = value;
   return MK_OK;
 }

@@ -1,7 +1,7 @@
-// Thin inline-PTX layer for sm_100a: mbarrier, TMA (tiled and untiled bulk copies, never with a
-// cluster-wide broadcast qualifier), tcgen05 MMA / TMEM, and scoped flag loads/stores used for
-// cross-CTA and cross-GPU signalling.  Everything here is a one-instruction wrapper; the protocol
-// built from them lives in gemm_core.cuh and fused_ops.cu.
+// Thin inline-PTX layer for sm_100a: mbarrier, TMA tile loads (never with a cluster-wide broadcast
+// qualifier), cp.async, tcgen05 MMA / TMEM, NVSwitch multimem accesses, and scoped flag
+// loads/stores used for cross-CTA and cross-GPU signalling.  Everything here is a one-instruction
+// wrapper; the protocol built from them lives in fused_kernel.cuh.
 #pragma once
 #include <cstdint>
 #include <cuda.h>
@@ -101,6 +101,11 @@ __device__ __forceinline__ void st_global_v4(void* p, uint4 v) {
                "r"(v.w)
                : "memory");
 }
+__device__ __forceinline__ void st_shared_v4(uint32_t addr, uint4 v) {
+  asm volatile("st.shared.v4.u32 [%0], {%1,%2,%3,%4};" ::"r"(addr), "r"(v.x), "r"(v.y), "r"(v.z),
+               "r"(v.w)
+               : "memory");
+}
 __device__ __forceinline__ uint4 ld_shared_v4(uint32_t addr) {
   uint4 v;
   asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];"
@@ -152,33 +157,6 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
 }
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
-}
-
-// ---------------------------------------------------------------- TMA: untiled bulk copies
-// global -> shared (source may be a mapped peer GPU address), completes bytes on an mbarrier.
-__device__ __forceinline__ void bulk_g2s(uint32_t dst, const void* src, uint32_t bytes,
-                                         uint32_t bar) {
-  asm volatile(
-      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
-      : "memory");
-}
-// shared -> global, tracked by the issuing thread's bulk async-group.
-__device__ __forceinline__ void bulk_s2g(void* dst, uint32_t src, uint32_t bytes) {
-  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst),
-               "r"(src), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ void bulk_commit() {
-  asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-}
-template <int N>
-__device__ __forceinline__ void bulk_wait_read() {
-  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
-}
-template <int N>
-__device__ __forceinline__ void bulk_wait_all() {
-  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
 }
 
 // ---------------------------------------------------------------- tcgen05 / TMEM

@@ -26,7 +26,10 @@ constexpr int kBlockM = 128;
 constexpr int kBlockK = 64;
 constexpr int kThreads = 256;
 constexpr int kGatherSub = 8;          // AllGather: a 128-row block lands as 8 groups of 16 rows
-constexpr int kRingVec = 40;           // exchange role: 16-byte ring slots per thread (160 KB/CTA)
+constexpr int kRingDedicated = 40;     // 16-byte ring slots per lane, warps of an exchange CTA
+constexpr int kRingInCta = 32;         // same for the exchange warp inside a compute CTA (16 KB)
+constexpr int kEpilogueStageBytes = 16384;  // 4 epilogue warps x 32 rows x 128 B transpose buffers
+constexpr int kInCtaRingBytes = kRingInCta * 32 * 16;
 constexpr int kMaxStages = 8;
 constexpr int kSmemBudget = 232448;    // 227 KiB opt-in limit per CTA on sm_100
 constexpr int kSmemBarrierBytes = 512;
@@ -39,7 +42,8 @@ enum SyncWord : int {
   SW_ENTRY = 0,       // [0,8): entry-barrier slot per source rank (AllGather prepare)
   SW_EPOCH = 8,       // device-resident epoch (AG: bumped by prepare; RS: bumped at kernel exit)
   SW_GRID_DONE = 9,   // CTAs that reached the end of the kernel (reset by the last one)
-  SW_COMM_DONE = 10,  // exchange CTAs that finished (reset by the last CTA)
+  SW_NEXT_ITEM = 10,  // next exchange work item to hand out (reset by the last CTA)
+  SW_ITEMS_DONE = 11, // exchange work items completed (reset by the last CTA)
   SW_STATUS = 12,     // [12,16): {code, where, detail0, detail1}; 0 = healthy
   SW_EXIT = 16,       // [16,24): exit slot per rank: "rank s finished its exchange role"
   SW_FLAGS = 64,      // per-tile / per-row-group flags start here
@@ -165,18 +169,46 @@ MKB_HD long long tile_flag_index(const Sched& s, int src, int rb, int q) {
 MKB_HD long long gather_flag_index(int rb, int sub) { return (long long)rb * kGatherSub + sub; }
 MKB_HD long long sync_words_needed(const Sched& s) {
   if (s.op == OP_AG) return SW_FLAGS + (long long)s.P * kGatherSub;
-  if (s.op == OP_RS || s.op == OP_AR) return SW_FLAGS + (long long)s.world * s.P * s.Q;
+  // per-tile flags of every source rank, then one "row-block complete" summary word per block
+  if (s.op == OP_RS || s.op == OP_AR) return SW_FLAGS + (long long)s.world * s.P * s.Q + s.P;
   return SW_FLAGS;
+}
+MKB_HD long long summary_flag_index(const Sched& s, int rb) {
+  return (long long)s.world * s.P * s.Q + rb;
+}
+
+// Exchange work items.  AllGather: one item = one 16-row group of the own shard for one
+// receiving rank (peer-major, nearest deadline first) or, through NVSwitch multicast, for all
+// ranks at once.  ReduceScatter / AllReduce: the rows an owner reduces, cut at row-block
+// boundaries into pieces and every piece into chunks of item_vecs 16-byte vectors.
+MKB_HD int gather_num_items(const Sched& s, int nvls) {
+  return (nvls ? 1 : s.world - 1) * s.part_blocks * kGatherSub;
+}
+MKB_HD int reduce_chunks_per_piece(const Sched& s, int item_vecs) {
+  int rows = s.part_rows < kBlockM ? s.part_rows : kBlockM;
+  long long vecs = (long long)rows * s.N / 8;
+  return (int)((vecs + item_vecs - 1) / item_vecs);
+}
+MKB_HD int reduce_num_items(const Sched& s, int owner, int item_vecs) {
+  return owner_num_items(s, owner) * reduce_chunks_per_piece(s, item_vecs);
+}
+MKB_HD int choose_item_vecs(const Sched& s, int workers) {
+  long long total = (long long)s.part_rows * s.N / 8;
+  long long v = total / (2LL * (workers > 0 ? workers : 1));
+  if (v < 128) v = 128;
+  if (v > 4096) v = 4096;
+  return (int)((v + 31) / 32 * 32);
 }
 
 // Shared-memory plan for one CTA.
 MKB_HD int stage_bytes(int block_n) { return kBlockM * kBlockK * 2 + block_n * kBlockK * 2; }
+constexpr int kSmemFixedBytes = 1024 + kSmemBarrierBytes + kEpilogueStageBytes + kInCtaRingBytes;
 MKB_HD int num_stages(int block_n) {
-  int n = (kSmemBudget - 1024 - kSmemBarrierBytes) / stage_bytes(block_n);
+  int n = (kSmemBudget - kSmemFixedBytes) / stage_bytes(block_n);
   return n > kMaxStages ? kMaxStages : n;
 }
 MKB_HD int smem_bytes(int block_n) {
-  return 1024 + num_stages(block_n) * stage_bytes(block_n) + kSmemBarrierBytes;
+  return kSmemFixedBytes + num_stages(block_n) * stage_bytes(block_n);
 }
 
 // Column-block width: pick the multiple of `quantum` in [64, 256] that minimises the number of

@@ -53,6 +53,8 @@ def test_options_roundtrip():
     _lib.set_option("wait_limit_ms", 4000)
     with pytest.raises(_lib.MkError):
         _lib.set_option("block_n", -5)
+    _lib.set_option("n_comm", 4)
+    _lib.set_option("n_comm", -1)          # back to the heuristic
 
 
 def test_view_validation_without_gpu():
