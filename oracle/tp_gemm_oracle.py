@@ -138,9 +138,11 @@ def rel_error(observed: torch.Tensor, expected: torch.Tensor,
     A plain elementwise relative error is unbounded where the reference crosses zero, so the
     denominator is floored at the RMS of the reference.  For the reduced operators the per-rank
     partial products travel as bf16 (that is the operator contract: the symmetric C buffer is
-    bf16), so each partial carries a rounding error proportional to ITS magnitude, which can
-    exceed the magnitude of the sum; `rounded_scale` = max over ranks of |partial| per element
-    then floors the denominator too.  The bound is 1e-2 in every case."""
+    bf16), so each partial carries a rounding error of up to 2^-8 of ITS magnitude, which can
+    exceed the magnitude of the sum when partials cancel; `rounded_scale` = sum over ranks of
+    |partial| per element (everything that was rounded on the way) then floors the denominator
+    too, which bounds the metric by 2 * 2^-8 for any world size.  The bound is 1e-2 in every
+    case."""
     o = observed.detach().double()
     e = expected.detach().double()
     if e.numel() == 0:

@@ -86,7 +86,7 @@ def case_rs(rank, world, M, N, K, seed, iters, max_rows, multicast=False):
         a, b = orc.synth_inputs("rs", r, world, M, N, K, seed=seed)
         p = a[rank * Ms + rows].float() @ b.float()
         ref = p if ref is None else ref + p
-        scale = p.abs() if scale is None else torch.maximum(scale, p.abs())
+        scale = p.abs() if scale is None else scale + p.abs()
         if r == rank:
             mine = (a, b)
     A = mine[0].to(dev)
@@ -124,7 +124,7 @@ def case_ar(rank, world, M, N, K, seed, iters, max_rows, layout=_lib.MK_B_KN, mu
         a, b = orc.synth_inputs("ar", r, world, M, N, K, seed=seed)
         p = a[rows].float() @ b.float()
         ref = p if ref is None else ref + p
-        scale = p.abs() if scale is None else torch.maximum(scale, p.abs())
+        scale = p.abs() if scale is None else scale + p.abs()
         if r == rank:
             mine, mine_partial = (a, b), p
     A = mine[0].to(dev)
