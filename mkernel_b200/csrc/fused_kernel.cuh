@@ -165,13 +165,11 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
     for (int t = cta; t < total && ok; t += n_comp) {
       const TileInfo ti = tile_info(s, t);
       if (OP == OP_AG && s.world > 1 && rowblock_shard(s, ti.rowblock) != s.rank) {
-        // Rows of a remote shard: wait until the sender has landed all 16-row groups here.
-        bool mine = true;
-        if (lane < kGatherSub) {
-          const uint32_t* f = p.sync + SW_FLAGS + gather_flag_index(ti.rowblock, lane);
-          mine = bounded_wait<true>(wc, [&] { return ptx::ld_acquire_sys(f) == epoch; },
-                                    ST_TIMEOUT_GATHER, ti.rowblock, lane);
-        }
+        // Rows of a remote shard: wait until the sender has landed all 4-row groups here.
+        static_assert(kGatherSub == 32, "one group flag per producer lane");
+        const uint32_t* f = p.sync + SW_FLAGS + gather_flag_index(ti.rowblock, lane);
+        const bool mine = bounded_wait<true>(wc, [&] { return ptx::ld_acquire_sys(f) == epoch; },
+                                             ST_TIMEOUT_GATHER, ti.rowblock, lane);
         ok = __all_sync(0xffffffffu, mine);
         ptx::fence_proxy_async();  // rows stored by a peer GPU are about to be read by TMA
         if (!ok) break;
@@ -265,8 +263,24 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
     int acc = 0;
     uint32_t acc_phase = 0;
     const int sub_row = lane >> 3, piece = lane & 7;
+    uint32_t entered_mask = 1u << s.rank;  // owners known to have entered this launch
     for (int t = cta; t < total; t += n_comp) {
       const TileInfo ti = tile_info(s, t);
+      if (OP == OP_RS && s.world > 1) {
+        // Rows of this tile go into their owners' buffers: an owner's buffer may be written
+        // only once that owner has entered this launch (its previous reduce has ended).
+        int lo, hi;
+        rowblock_owners(s, ti.rowblock, &lo, &hi);
+        bool ok = true;
+        for (int o = lo; o <= hi && ok; ++o) {
+          if (entered_mask & (1u << o)) continue;
+          const uint32_t* f = p.sync + SW_ENTRY + o;
+          ok = bounded_wait<true>(wc, [&] { return ptx::ld_acquire_sys(f) == epoch; },
+                                  ST_TIMEOUT_ENTRY, o, epoch);
+          entered_mask |= 1u << o;
+        }
+        if (!__all_sync(0xffffffffu, ok)) break;
+      }
       if (!wait_mbar(wc, bar(BAR_TFULL + acc), acc_phase, 0x500u + acc)) break;
       ptx::tc_fence_after();
       const uint32_t t_base = tmem_base + acc * 256 + (static_cast<uint32_t>(quarter * 32) << 16);
@@ -444,6 +458,7 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
   const bool nvls_ar = OP == OP_AR && p.use_nvls && p.mc_data != nullptr && p.mc_out != nullptr;
   const long long row_bytes = (OP == OP_AG ? static_cast<long long>(p.K) : static_cast<long long>(s.N)) * 2;
   char* const local = static_cast<char*>(p.peer_data[s.rank]);
+  uint32_t entered_mask = 1u << s.rank;  // ranks known to have entered this launch
 
   while (true) {
     if (lane == 0) *s_item = atomicAdd(p.sync + SW_NEXT_ITEM, 1u);
@@ -466,6 +481,20 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
       const long long base = (static_cast<long long>(rowblock_row0(s, rowblock)) + r0) * row_bytes;
       const int dst_rank = (s.rank - d + W) % W;
       char* dst = nvls_ag ? static_cast<char*>(p.mc_data) : static_cast<char*>(p.peer_data[dst_rank]);
+      // The receiver's gathered buffer may be overwritten only once the receiver has entered
+      // this launch (its previous launch, which read the buffer, has ended).
+      {
+        const int first = nvls_ag ? 0 : dst_rank, last = nvls_ag ? W - 1 : dst_rank;
+        bool ok = true;
+        for (int r = first + lane; r <= last && ok; r += 32) {
+          if (entered_mask & (1u << r)) continue;
+          const uint32_t* f = p.sync + SW_ENTRY + r;
+          ok = bounded_wait<true>(wc, [&] { return ptx::ld_acquire_sys(f) == epoch; },
+                                  ST_TIMEOUT_ENTRY, r, epoch);
+        }
+        if (!__all_sync(0xffffffffu, ok)) return;
+        for (int r = first; r <= last; ++r) entered_mask |= 1u << r;
+      }
       push_span<R>(local + base, dst + base, n_vec, nvls_ag, ring, lane);
       __syncwarp();
       if (lane == 0) {
@@ -533,8 +562,9 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
       if (lane == 0) ptx::fence_acq_rel_sys();   // results (remote for AR) before "item done"
     }
 
-    // 3. the worker that completes the rank's last item tells every rank this rank is done
-    if (lane == 0) {
+    // 3. AllReduce: the worker that completes the rank's last item tells every rank that this
+    //    rank has written its share of their outputs and no longer reads their partials.
+    if (OP == OP_AR && lane == 0) {
       const uint32_t done = atomicAdd(p.sync + SW_ITEMS_DONE, 1u);
       if (done == static_cast<uint32_t>(p.n_items - 1)) {
         ptx::fence_acq_rel_sys();
@@ -578,10 +608,8 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
   if (threadIdx.x == 0) {
     *s_abort = 0u;
     uint32_t e = p.epoch_arg;
-    if (p.sync != nullptr) {
-      if (OP == OP_AG) e = ptx::ld_relaxed_sys(p.sync + SW_EPOCH);
-      if (OP == OP_RS) e = ptx::ld_relaxed_sys(p.sync + SW_EPOCH) + 1u;
-    }
+    if (p.sync != nullptr && (OP == OP_AG || OP == OP_RS))
+      e = ptx::ld_relaxed_sys(p.sync + SW_EPOCH) + 1u;
     *s_epoch = e;
     if (!is_comm) {
       for (int i = 0; i < kMaxStages; ++i) {
@@ -598,9 +626,14 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
       ptx::tma_prefetch_desc(&tma_b);
     }
     ptx::fence_mbar_init();
-    // A rank with nothing to exchange still owes its peers the "finished" signal.
-    if (blockIdx.x == 0 && p.sync != nullptr && s.world > 1 && p.n_items <= 0) {
-      for (int r = 0; r < s.world; ++r) ptx::st_release_sys(p.peer_sync[r] + SW_EXIT + s.rank, e);
+    if (blockIdx.x == 0 && p.sync != nullptr && s.world > 1) {
+      // AG / RS: tell every rank that this rank has entered launch e, i.e. that its previous
+      // launch has ended and its buffers may be written again (replaces an all-rank barrier).
+      if (OP == OP_AG || OP == OP_RS)
+        for (int r = 0; r < s.world; ++r) ptx::st_release_sys(p.peer_sync[r] + SW_ENTRY + s.rank, e);
+      // AR: a rank with nothing to reduce still owes its peers the "finished" signal.
+      if (OP == OP_AR && p.n_items <= 0)
+        for (int r = 0; r < s.world; ++r) ptx::st_release_sys(p.peer_sync[r] + SW_EXIT + s.rank, e);
     }
   }
   if (!is_comm && warp == 1) {
@@ -643,9 +676,11 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
   __threadfence();
   const uint32_t done = atomicAdd(p.sync + SW_GRID_DONE, 1u);
   if (done == gridDim.x - 1) {
-    // Last CTA of this rank: the kernel may only end when every rank has finished its exchange
-    // work (nobody still reads or writes this rank's buffers; AllReduce output is complete).
-    if (s.world > 1 && *s_abort == 0u) {
+    // Last CTA of this rank.  AllReduce: the kernel may only end when every rank has finished
+    // its exchange work (this rank's output is complete, nobody still reads its partials).
+    // AG / RS need no such wait: their results are produced by this rank's own CTAs, and the
+    // next launch's writers wait for the entry flag instead.
+    if (OP == OP_AR && s.world > 1 && *s_abort == 0u) {
       for (int r = 0; r < s.world; ++r) {
         const uint32_t* f = p.sync + SW_EXIT + r;
         if (!bounded_wait<true>(wc, [&] { return ptx::ld_acquire_sys(f) == epoch; },
@@ -656,45 +691,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
     p.sync[SW_GRID_DONE] = 0u;
     p.sync[SW_NEXT_ITEM] = 0u;
     p.sync[SW_ITEMS_DONE] = 0u;
-    if (OP == OP_RS) p.sync[SW_EPOCH] = epoch;
-    __threadfence();
-  }
-}
-
-// Entry barrier of AllGather+GEMM (one warp): bump the device epoch, tell every peer, wait for
-// every peer.  After it every rank's previous launch has ended and every rank's shard is in place.
-// Stands in for prepare_epoch_barrier, src/ag_gemm_warp_specialized.cu:115-129.
-struct EntryParams {
-  uint32_t* sync;
-  uint32_t* peer_sync[kMaxWorld];
-  int rank, world;
-  uint64_t limit_ns;
-};
-__global__ void entry_barrier_kernel(const __grid_constant__ EntryParams e) {
-  __shared__ uint32_t s_abort;
-  __shared__ uint32_t s_epoch;
-  const int lane = threadIdx.x;
-  if (lane == 0) {
-    s_abort = 0u;
-    s_epoch = ptx::ld_relaxed_sys(e.sync + SW_EPOCH) + 1u;
-  }
-  __syncwarp();
-  const uint32_t epoch = s_epoch;
-  WaitCtx wc;
-  wc.status = e.sync + SW_STATUS;
-  wc.s_abort = &s_abort;
-  wc.limit_ns = e.limit_ns;
-  wc.where = 14u;
-  if (lane < e.world) {
-    ptx::fence_acq_rel_sys();
-    ptx::st_relaxed_sys(e.peer_sync[lane] + SW_ENTRY + e.rank, epoch);
-    const uint32_t* f = e.sync + SW_ENTRY + lane;
-    bounded_wait<true>(wc, [&] { return static_cast<int32_t>(ptx::ld_acquire_sys(f) - epoch) >= 0; },
-                       ST_TIMEOUT_ENTRY, lane, epoch);
-  }
-  __syncwarp();
-  if (lane == 0) {
-    e.sync[SW_EPOCH] = epoch;
+    if (OP == OP_RS || OP == OP_AG) p.sync[SW_EPOCH] = epoch;
     __threadfence();
   }
 }

@@ -340,24 +340,13 @@ int mk_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int
 }
 
 int mk_ag_gemm_prepare(const mk_symm_view* ready, void* stream) {
-  int rc = check_view(ready, "ready", (size_t)MK_AG_READY_WORDS * 4);
-  if (rc != MK_OK) return rc;
-  EntryParams e;
-  memset(&e, 0, sizeof(e));
-  e.sync = static_cast<uint32_t*>(ready->peer[ready->rank]);
-  for (int r = 0; r < ready->world; ++r) {
-    if (!ready->peer[r]) return set_error(MK_ERR_INVALID, "ready: no address for rank %d", r);
-    e.peer_sync[r] = static_cast<uint32_t*>(ready->peer[r]);
-  }
-  e.rank = ready->rank;
-  e.world = ready->world;
-  {
-    std::lock_guard<std::mutex> g(g_opt_mu);
-    e.limit_ns = (uint64_t)g_opt.wait_limit_ms * 1000000ull;
-  }
-  entry_barrier_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(e);
-  MKB_CUDA(cudaGetLastError());
-  return MK_OK;
+  // The reference runs an all-rank barrier kernel here (src/ag_gemm_warp_specialized.cu:115-134).
+  // In this design the launch itself carries the ordering: every rank announces "entered launch
+  // e" to its peers when its kernel starts, and nobody writes into a peer's gathered buffer
+  // before seeing that announcement.  prepare therefore only validates its argument; it is kept
+  // so that callers written against the reference run unchanged.
+  (void)stream;
+  return check_view(ready, "ready", (size_t)MK_AG_READY_WORDS * 4);
 }
 
 int mk_ag_gemm_launch(const mk_symm_view* A, const mk_symm_view* ready, const void* B, void* C,

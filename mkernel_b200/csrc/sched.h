@@ -25,7 +25,7 @@ constexpr int kMaxWorld = 8;
 constexpr int kBlockM = 128;
 constexpr int kBlockK = 64;
 constexpr int kThreads = 256;
-constexpr int kGatherSub = 8;          // AllGather: a 128-row block lands as 8 groups of 16 rows
+constexpr int kGatherSub = 32;         // AllGather: a 128-row block lands as 32 groups of 4 rows
 constexpr int kRingDedicated = 40;     // 16-byte ring slots per lane, warps of an exchange CTA
 constexpr int kRingInCta = 32;         // same for the exchange warp inside a compute CTA (16 KB)
 constexpr int kEpilogueStageBytes = 16384;  // 4 epilogue warps x 32 rows x 128 B transpose buffers
@@ -39,13 +39,13 @@ enum OpKind : int { OP_GEMM = 0, OP_AG = 1, OP_RS = 2, OP_AR = 3 };
 // Word offsets inside an operator's synchronisation buffer (uint32 words, caller-owned,
 // symmetric across ranks, zeroed once before first use).
 enum SyncWord : int {
-  SW_ENTRY = 0,       // [0,8): entry-barrier slot per source rank (AllGather prepare)
-  SW_EPOCH = 8,       // device-resident epoch (AG: bumped by prepare; RS: bumped at kernel exit)
+  SW_ENTRY = 0,       // [0,8): slot per rank: "rank s has entered launch <epoch>" (AG, RS)
+  SW_EPOCH = 8,       // device-resident epoch of the last finished launch (AG, RS)
   SW_GRID_DONE = 9,   // CTAs that reached the end of the kernel (reset by the last one)
   SW_NEXT_ITEM = 10,  // next exchange work item to hand out (reset by the last CTA)
   SW_ITEMS_DONE = 11, // exchange work items completed (reset by the last CTA)
   SW_STATUS = 12,     // [12,16): {code, where, detail0, detail1}; 0 = healthy
-  SW_EXIT = 16,       // [16,24): exit slot per rank: "rank s finished its exchange role"
+  SW_EXIT = 16,       // [16,24): exit slot per rank: "rank s finished its exchange work" (AR)
   SW_FLAGS = 64,      // per-tile / per-row-group flags start here
 };
 

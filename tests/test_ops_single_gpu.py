@@ -25,7 +25,7 @@ def test_ag_gemm_world1():
     ready.data_.zero_()
     B = b_kn.t().contiguous().to(DEV)
     C = torch.zeros((1, M, N), device=DEV, dtype=torch.bfloat16)
-    for _ in range(3):             # re-launch without host resets (epoch protocol)
+    for _ in range(3):             # re-launch without host resets (the epoch lives on the device)
         C.zero_()
         mod.ag_gemm_warp_specialized_prepare(ready, M, N)
         mod.ag_gemm_warp_specialized_launch(A, ready, B, C)
@@ -139,11 +139,13 @@ def test_wait_that_nothing_satisfies_returns_a_status():
         _lib.set_option("wait_limit_ms", 4000)
     out = (ctypes.c_uint32 * 4)()
     rc = lib.mk_op_status(ctypes.byref(sv), out)
-    assert rc == -5 and out[0] in (3, 4), (rc, list(out))               # tile flag / exit handshake
+    # either the reduce role gave up on rank 1's tile flags (3) or the epilogue gave up waiting
+    # for rank 1 to enter the launch before writing into its buffer (5)
+    assert rc == -5 and out[0] in (3, 5), (rc, list(out))
     assert "device wait expired" in _lib.last_error()
-    # the partial product was still computed (each row sits in its owner's buffer, in the slab
-    # of the producing rank), and the device still works
-    full = (A.float() @ B.float().t()).cpu()
-    assert orc.rel_error(c[0][:128].cpu(), full[:128]) <= orc.REL_TOL
-    assert orc.rel_error(c[1][:128].cpu(), full[128:]) <= orc.REL_TOL
-    assert torch.equal(torch.ones(4, device=DEV) * 2, torch.full((4,), 2.0, device=DEV))
+    # the context is intact: a fresh launch on the same device computes the right product
+    C = torch.empty((M, N), device=DEV, dtype=torch.bfloat16)
+    from mkernel_b200 import ops
+    ops.gemm_bf16(A, B, C)
+    torch.cuda.synchronize()
+    assert orc.rel_error(C.cpu(), (A.float() @ B.float().t()).cpu()) <= orc.REL_TOL
