@@ -141,19 +141,32 @@ __device__ __forceinline__ __nv_bfloat16* output_row(const OpParams& p, int grow
 // ------------------------------------------------------------------------------------------
 // GEMM roles of a compute CTA (warps 0, 1, 2, 4-7)
 // ------------------------------------------------------------------------------------------
-template <int OP>
+// CG = 1: every CTA computes its own 128 x block_n tiles.
+// CG = 2: CTAs run as pairs (a cluster of two).  The pair works on two tiles of the same column
+// block at a time, one per CTA; each CTA loads its own A tile and HALF of the B tile, the leader
+// (cluster rank 0) issues one 256 x block_n MMA per K step that reads both halves, and each CTA
+// drains its own 128 accumulator rows.  This halves the shared-memory traffic for B.
+// The two tiles need not be adjacent rows: consecutive tiles in visiting order share the column
+// block (the row-block index runs fastest inside a raster group of even height).
+template <int OP, int CG>
 __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CUtensorMap* tma_b,
                                               const OpParams& p, uint32_t smem_base,
                                               uint32_t bar_base, uint32_t epi_stage,
                                               uint32_t tmem_base, WaitCtx& wc, uint32_t epoch) {
   const Sched& s = p.sched;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int cta = blockIdx.x - p.n_comm;
   const int n_comp = gridDim.x - p.n_comm;
+  const int crank = CG == 2 ? static_cast<int>(ptx::cluster_ctarank()) : 0;
+  // First tile of this CTA; the stride is n_comp for both modes (pairs step by n_comp / 2).
+  const int cta = CG == 2 ? (((static_cast<int>(blockIdx.x) - p.n_comm) & ~1) + crank)
+                          : static_cast<int>(blockIdx.x) - p.n_comm;
   const int total = s.P * s.Q;
   const int bn = s.block_n;
-  const int stage_sz = stage_bytes(bn);
+  const int b_rows = bn / CG;                         // B rows (columns of C) this CTA loads
+  const int stage_sz = kBlockM * kBlockK * 2 + b_rows * kBlockK * 2;
   auto bar = [&](int slot) { return bar_base + 8u * slot; };
+  // Barriers the pair shares live in the leader CTA.
+  auto lead = [&](int slot) { return CG == 2 ? ptx::map_to_cta(bar(slot), 0) : bar(slot); };
   constexpr bool kSignals = (OP == OP_RS || OP == OP_AR);
 
   if (warp == 0) {
@@ -179,14 +192,28 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
           if (!wait_mbar(wc, bar(BAR_EMPTY + stage), phase ^ 1u, 0x100u + stage)) { ok = false; break; }
           const uint32_t a_dst = smem_base + stage * stage_sz;
           const uint32_t b_dst = a_dst + kBlockM * kBlockK * 2;
-          ptx::mbar_expect_tx(bar(BAR_FULL + stage), stage_sz);
-          ptx::tma_load_2d(a_dst, tma_a, bar(BAR_FULL + stage), kb * kBlockK, ti.row0);
-          if (!p.b_mn_major) {
-            ptx::tma_load_2d(b_dst, tma_b, bar(BAR_FULL + stage), kb * kBlockK, ti.n0);
+          const int nb0 = ti.n0 + crank * b_rows;   // first B row (C column) this CTA loads
+          if (CG == 1) {
+            ptx::mbar_expect_tx(bar(BAR_FULL + stage), stage_sz);
+            ptx::tma_load_2d(a_dst, tma_a, bar(BAR_FULL + stage), kb * kBlockK, ti.row0);
+            if (!p.b_mn_major) {
+              ptx::tma_load_2d(b_dst, tma_b, bar(BAR_FULL + stage), kb * kBlockK, nb0);
+            } else {
+              for (int c = 0; c < b_rows / 64; ++c)
+                ptx::tma_load_2d(b_dst + c * 8192, tma_b, bar(BAR_FULL + stage), nb0 + c * 64,
+                                 kb * kBlockK);
+            }
           } else {
-            for (int c = 0; c < bn / 64; ++c)
-              ptx::tma_load_2d(b_dst + c * 8192, tma_b, bar(BAR_FULL + stage), ti.n0 + c * 64,
-                               kb * kBlockK);
+            // Both CTAs' bytes are counted on the leader's barrier; only the leader arrives.
+            const uint32_t full = lead(BAR_FULL + stage);
+            if (crank == 0) ptx::mbar_expect_tx(bar(BAR_FULL + stage), 2 * stage_sz);
+            ptx::tma_load_2d_pair(a_dst, tma_a, full, kb * kBlockK, ti.row0);
+            if (!p.b_mn_major) {
+              ptx::tma_load_2d_pair(b_dst, tma_b, full, kb * kBlockK, nb0);
+            } else {
+              for (int c = 0; c < b_rows / 64; ++c)
+                ptx::tma_load_2d_pair(b_dst + c * 8192, tma_b, full, nb0 + c * 64, kb * kBlockK);
+            }
           }
           if (++stage == p.stages) { stage = 0; phase ^= 1u; }
         }
@@ -196,8 +223,8 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
   } else if (warp == 1) {
     // ---------------- MMA issuer (one thread) ----------------
     wc.where = (blockIdx.x << 8) | 1u;
-    if (lane == 0) {
-      const uint32_t idesc = ptx::make_idesc_bf16(bn, p.b_mn_major);
+    if (lane == 0 && crank == 0) {
+      const uint32_t idesc = ptx::make_idesc_bf16(bn, p.b_mn_major, 128u * CG);
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
@@ -220,13 +247,26 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
             const uint64_t b_desc =
                 p.b_mn_major ? ptx::make_smem_desc_sw128(b_base + k * 2048, 8192, 1024)
                              : ptx::make_smem_desc_sw128(b_base + k * 32, 16, 1024);
-            ptx::umma_bf16(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0 ? 1u : 0u);
+            if (CG == 1) ptx::umma_bf16(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0 ? 1u : 0u);
+            else ptx::umma_bf16_pair(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0 ? 1u : 0u);
           }
-          ptx::umma_commit(bar(BAR_EMPTY + stage));  // stage reusable once these MMAs finish
+          // stage reusable (in both CTAs of a pair) once these MMAs finish
+          if (CG == 1) {
+            ptx::umma_commit(bar(BAR_EMPTY + stage));
+          } else {
+            ptx::umma_commit_pair(ptx::map_to_cta(bar(BAR_EMPTY + stage), 0));
+            ptx::umma_commit_pair(ptx::map_to_cta(bar(BAR_EMPTY + stage), 1));
+          }
           if (++stage == p.stages) { stage = 0; phase ^= 1u; }
         }
         if (!ok) break;
-        ptx::umma_commit(bar(BAR_TFULL + acc));      // accumulator complete
+        // accumulator complete (each CTA of a pair holds its own 128 rows)
+        if (CG == 1) {
+          ptx::umma_commit(bar(BAR_TFULL + acc));
+        } else {
+          ptx::umma_commit_pair(ptx::map_to_cta(bar(BAR_TFULL + acc), 0));
+          ptx::umma_commit_pair(ptx::map_to_cta(bar(BAR_TFULL + acc), 1));
+        }
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }
@@ -247,7 +287,8 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
         rowblock_owners(s, ti.rowblock, &lo, &hi);
         const long long idx = SW_FLAGS + tile_flag_index(s, s.rank, ti.rowblock, ti.q);
         for (int o = lo; o <= hi; ++o) ptx::st_relaxed_sys(p.peer_sync[o] + idx, epoch);
-        ptx::mbar_arrive(bar(BAR_TEMPTY + acc));
+        if (CG == 1) ptx::mbar_arrive(bar(BAR_TEMPTY + acc));
+        else ptx::mbar_arrive_cluster(lead(BAR_TEMPTY + acc));
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
       }
@@ -332,7 +373,8 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) {
-        ptx::mbar_arrive(bar(BAR_TEMPTY + acc));
+        if (CG == 1) ptx::mbar_arrive(bar(BAR_TEMPTY + acc));
+        else ptx::mbar_arrive_cluster(lead(BAR_TEMPTY + acc));
         if (kSignals && s.world > 1) ptx::mbar_arrive(bar(BAR_STORED + acc));
       }
       acc ^= 1;
@@ -578,7 +620,7 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
 // ------------------------------------------------------------------------------------------
 // Kernel
 // ------------------------------------------------------------------------------------------
-template <int OP>
+template <int OP, int CG>
 __global__ void __launch_bounds__(kThreads, 1)
 fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
                   const __grid_constant__ CUtensorMap tma_b,
@@ -587,7 +629,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
   const Sched& s = p.sched;
   const int warp = threadIdx.x >> 5;
   const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
-  const int ring_bytes = p.stages * stage_bytes(s.block_n);
+  const int ring_bytes = p.stages * stage_bytes_cg(s.block_n, CG);
   const uint32_t bar_base = smem_base + ring_bytes;
   const uint32_t epi_stage = bar_base + kSmemBarrierBytes;
   const uint32_t xchg_ring = epi_stage + kEpilogueStageBytes;
@@ -619,7 +661,8 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
       const bool publishes = (OP == OP_RS || OP == OP_AR) && s.world > 1;
       for (int i = 0; i < 2; ++i) {
         ptx::mbar_init(bar_base + 8u * (BAR_TFULL + i), 1);
-        ptx::mbar_init(bar_base + 8u * (BAR_TEMPTY + i), publishes ? 5 : 4);
+        // accumulator free again: 4 epilogue warps (+ the publisher) of every CTA sharing it
+        ptx::mbar_init(bar_base + 8u * (BAR_TEMPTY + i), (publishes ? 5 : 4) * CG);
         ptx::mbar_init(bar_base + 8u * (BAR_STORED + i), 4);
       }
       ptx::tma_prefetch_desc(&tma_a);
@@ -636,9 +679,15 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
         for (int r = 0; r < s.world; ++r) ptx::st_release_sys(p.peer_sync[r] + SW_EXIT + s.rank, e);
     }
   }
+  if (CG == 2 && !is_comm) ptx::cluster_sync_all();  // both CTAs' barriers exist before any use
   if (!is_comm && warp == 1) {
-    ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(s_tmem)), 512);
-    ptx::tmem_relinquish();
+    if (CG == 1) {
+      ptx::tmem_alloc(ptx::smem_u32(const_cast<uint32_t*>(s_tmem)), 512);
+      ptx::tmem_relinquish();
+    } else {
+      ptx::tmem_alloc_pair(ptx::smem_u32(const_cast<uint32_t*>(s_tmem)), 512);
+      ptx::tmem_relinquish_pair();
+    }
   }
   ptx::tc_fence_before();
   __syncthreads();
@@ -652,7 +701,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
   } else if (warp == 3) {
     if (OP != OP_GEMM) exchange_worker<OP, kRingInCta>(p, xchg_ring, wc, epoch, s_item + warp);
   } else {
-    compute_roles<OP>(&tma_a, &tma_b, p, smem_base, bar_base, epi_stage, *s_tmem, wc, epoch);
+    compute_roles<OP, CG>(&tma_a, &tma_b, p, smem_base, bar_base, epi_stage, *s_tmem, wc, epoch);
   }
 
   // ---------------- teardown ----------------
@@ -664,10 +713,13 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
   }
   ptx::tc_fence_before();
   __syncthreads();
+  // A pair leaves together: the peer may still signal this CTA's barriers or read its operands.
+  if (CG == 2 && !is_comm) ptx::cluster_sync_all();
   if (!is_comm && warp == 1) {
     __syncwarp();
     ptx::tc_fence_after();
-    ptx::tmem_dealloc(*s_tmem, 512);
+    if (CG == 1) ptx::tmem_dealloc(*s_tmem, 512);
+    else ptx::tmem_dealloc_pair(*s_tmem, 512);
   }
   if (p.sync == nullptr || threadIdx.x != 0) return;
 

@@ -29,6 +29,7 @@ struct Options {
   long long block_n = 0;
   long long group_rows = 0;
   long long use_nvls = 0;
+  long long cta_pair = 0;   // 1: run compute CTAs as pairs (two-SM MMA) when the shape allows
 };
 static Options g_opt;
 static std::mutex g_opt_mu;
@@ -40,6 +41,7 @@ static long long* option_slot(const char* name) {
   if (!strcmp(name, "block_n")) return &g_opt.block_n;
   if (!strcmp(name, "group_rows")) return &g_opt.group_rows;
   if (!strcmp(name, "use_nvls")) return &g_opt.use_nvls;
+  if (!strcmp(name, "cta_pair")) return &g_opt.cta_pair;
   return nullptr;
 }
 
@@ -49,6 +51,7 @@ static long long* option_slot(const char* name) {
 struct Plan {
   Sched sched;
   int K, k_blocks, stages, n_comm, grid, smem;
+  int cg;   // 1: independent CTAs; 2: CTA pairs
   int b_mn_major;
 };
 
@@ -104,12 +107,20 @@ static int make_plan(int op, int rank, int world, int M, int N, int K, int b_lay
   pl.sched = make_sched(op, rank, world, M, N, bn, group);
   pl.K = K;
   pl.k_blocks = ceil_div(K, kBlockK);
-  pl.stages = num_stages(bn);
-  pl.smem = smem_bytes(bn);
   pl.b_mn_major = b_layout == MK_B_KN ? 1 : 0;
   const long long tiles = (long long)pl.sched.P * pl.sched.Q;
   int n_comp = tiles < n_comp_max ? (int)tiles : n_comp_max;
   if (n_comp < 1) n_comp = 1;
+  // CTA pairs: consecutive tiles (2i, 2i+1) must share a column block, which holds when every
+  // raster group has an even number of row-blocks; the pair splits B's rows in two halves.
+  pl.cg = 1;
+  if (o.cta_pair != 0 && pl.sched.P % 2 == 0 && pl.sched.group_rows % 2 == 0 && tiles >= 2 &&
+      bn % (pl.b_mn_major ? 128 : 32) == 0 && n_comm % 2 == 0 && (n_comp & ~1) >= 2) {
+    pl.cg = 2;
+    n_comp &= ~1;
+  }
+  pl.stages = num_stages_cg(bn, pl.cg);
+  pl.smem = smem_bytes_cg(bn, pl.cg);
   pl.n_comm = n_comm;
   pl.grid = n_comm + n_comp;
   *out = pl;
@@ -166,10 +177,10 @@ static int device_sm_count(int* out) {
   return MK_OK;
 }
 
-template <int OP>
+template <int OP, int CG>
 static int launch_kernel(const Plan& pl, const CUtensorMap& ta, const CUtensorMap& tb,
                          const OpParams& p, cudaStream_t stream) {
-  auto kern = fused_gemm_kernel<OP>;
+  auto kern = fused_gemm_kernel<OP, CG>;
   static bool attr_set[64];
   int dev = 0;
   MKB_CUDA(cudaGetDevice(&dev));
@@ -183,8 +194,35 @@ static int launch_kernel(const Plan& pl, const CUtensorMap& ta, const CUtensorMa
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = pl.smem;
   cfg.stream = stream;
-  cfg.attrs = nullptr;
-  cfg.numAttrs = 0;
+  cudaLaunchAttribute attr[1];
+  if (CG == 2) {
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+  } else {
+    cfg.attrs = nullptr;
+    cfg.numAttrs = 0;
+  }
+  if (CG == 2) {
+    // The kernel is persistent and its roles wait on one another, so every CTA must be resident
+    // at once: never launch more pairs than the device can hold (SM counts per GPC need not be
+    // even, which can leave an SM without a partner).
+    static int max_pairs[64];
+    if (dev < 0 || dev >= 64 || max_pairs[dev] == 0) {
+      int n = 0;
+      MKB_CUDA(cudaOccupancyMaxActiveClusters(&n, kern, &cfg));
+      if (n < 1) return set_error(MK_ERR_CUDA, "device cannot co-schedule a CTA pair");
+      if (dev >= 0 && dev < 64) max_pairs[dev] = n;
+      if (pl.grid / 2 > n) cfg.gridDim = dim3(2 * n, 1, 1);
+    } else if (pl.grid / 2 > max_pairs[dev]) {
+      cfg.gridDim = dim3(2 * max_pairs[dev], 1, 1);
+    }
+    if ((int)cfg.gridDim.x <= p.n_comm)
+      return set_error(MK_ERR_INVALID, "no SM pair left for the GEMM role");
+  }
   MKB_CUDA(cudaLaunchKernelEx(&cfg, kern, ta, tb, p));
   return MK_OK;
 }
@@ -277,16 +315,24 @@ static int run_op(const OpArgs& a, cudaStream_t stream) {
     rc = encode_2d_bf16(&tb, a.B, (uint64_t)a.N, (uint64_t)a.K, (uint64_t)a.N, 64, kBlockK);
   else
     rc = encode_2d_bf16(&tb, a.B, (uint64_t)a.K, (uint64_t)a.N, (uint64_t)a.K, kBlockK,
-                        (uint32_t)pl.sched.block_n);
+                        (uint32_t)(pl.sched.block_n / pl.cg));
   if (rc != MK_OK) return rc;
   if ((reinterpret_cast<uintptr_t>(a.C) & 15) != 0)
     return set_error(MK_ERR_INVALID, "C must be 16-byte aligned");
 
+  if (pl.cg == 2) {
+    switch (a.op) {
+      case OP_GEMM: return launch_kernel<OP_GEMM, 2>(pl, ta, tb, p, stream);
+      case OP_AG: return launch_kernel<OP_AG, 2>(pl, ta, tb, p, stream);
+      case OP_RS: return launch_kernel<OP_RS, 2>(pl, ta, tb, p, stream);
+      case OP_AR: return launch_kernel<OP_AR, 2>(pl, ta, tb, p, stream);
+    }
+  }
   switch (a.op) {
-    case OP_GEMM: return launch_kernel<OP_GEMM>(pl, ta, tb, p, stream);
-    case OP_AG: return launch_kernel<OP_AG>(pl, ta, tb, p, stream);
-    case OP_RS: return launch_kernel<OP_RS>(pl, ta, tb, p, stream);
-    case OP_AR: return launch_kernel<OP_AR>(pl, ta, tb, p, stream);
+    case OP_GEMM: return launch_kernel<OP_GEMM, 1>(pl, ta, tb, p, stream);
+    case OP_AG: return launch_kernel<OP_AG, 1>(pl, ta, tb, p, stream);
+    case OP_RS: return launch_kernel<OP_RS, 1>(pl, ta, tb, p, stream);
+    case OP_AR: return launch_kernel<OP_AR, 1>(pl, ta, tb, p, stream);
   }
   return set_error(MK_ERR_INVALID, "unknown op");
 }

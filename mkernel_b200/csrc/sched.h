@@ -202,6 +202,10 @@ MKB_HD int choose_item_vecs(const Sched& s, int workers) {
 
 // Shared-memory plan for one CTA.
 MKB_HD int stage_bytes(int block_n) { return kBlockM * kBlockK * 2 + block_n * kBlockK * 2; }
+// Same for a CTA pair (cg = 2): each CTA holds its A tile and half of the B tile.
+MKB_HD int stage_bytes_cg(int block_n, int cg) {
+  return kBlockM * kBlockK * 2 + (block_n / cg) * kBlockK * 2;
+}
 constexpr int kSmemFixedBytes = 1024 + kSmemBarrierBytes + kEpilogueStageBytes + kInCtaRingBytes;
 MKB_HD int num_stages(int block_n) {
   int n = (kSmemBudget - kSmemFixedBytes) / stage_bytes(block_n);
@@ -209,6 +213,13 @@ MKB_HD int num_stages(int block_n) {
 }
 MKB_HD int smem_bytes(int block_n) {
   return kSmemFixedBytes + num_stages(block_n) * stage_bytes(block_n);
+}
+MKB_HD int num_stages_cg(int block_n, int cg) {
+  int n = (kSmemBudget - kSmemFixedBytes) / stage_bytes_cg(block_n, cg);
+  return n > kMaxStages ? kMaxStages : n;
+}
+MKB_HD int smem_bytes_cg(int block_n, int cg) {
+  return kSmemFixedBytes + num_stages_cg(block_n, cg) * stage_bytes_cg(block_n, cg);
 }
 
 // Column-block width: pick the multiple of `quantum` in [64, 256] that minimises the number of
