@@ -141,7 +141,8 @@ int mk_op_status_clear(const mk_symm_view* sync, void* stream);
 
 /* ---- options (process-wide): "wait_limit_ms" (device wait budget, default 4000),
  *      "n_comm" (dedicated exchange CTAs, -1 = heuristic), "block_n" (0 = heuristic), "group_rows",
- *      "use_nvls" (0/1: reduce through NVSwitch multicast when the buffers have an alias). */
+ *      "use_nvls" (0/1: exchange through NVSwitch multicast when the buffers have an alias),
+ *      "cta_pair" (0/1, default 1: two-SM MMA over CTA pairs when the shape allows). */
 int mk_set_option(const char* name, long long value);
 long long mk_get_option(const char* name);
 

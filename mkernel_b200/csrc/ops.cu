@@ -29,7 +29,7 @@ struct Options {
   long long block_n = 0;
   long long group_rows = 0;
   long long use_nvls = 0;
-  long long cta_pair = 0;   // 1: run compute CTAs as pairs (two-SM MMA) when the shape allows
+  long long cta_pair = 1;   // 1: run compute CTAs as pairs (two-SM MMA) when the shape allows
 };
 static Options g_opt;
 static std::mutex g_opt_mu;

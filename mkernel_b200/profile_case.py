@@ -23,6 +23,7 @@ def main() -> None:
     ap.add_argument("--iters", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=2)
     ap.add_argument("--block-n", type=int, default=0)
+    ap.add_argument("--cta-pair", type=int, default=1)
     args = ap.parse_args()
     M, N, K = args.m, args.n, args.k
     dev = torch.device("cuda", 0)
@@ -31,6 +32,7 @@ def main() -> None:
     A = torch.randn((M, K), device=dev, generator=g).to(torch.bfloat16)
     B_nk = (torch.randn((N, K), device=dev, generator=g) * K ** -0.5).to(torch.bfloat16)
     _lib.set_option("block_n", args.block_n)
+    _lib.set_option("cta_pair", args.cta_pair)
 
     if args.op == "gemm":
         C = torch.empty((M, N), device=dev, dtype=torch.bfloat16)
