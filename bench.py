@@ -5,7 +5,7 @@
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
         --master-port P bench.py --gpus N --steps K --warmup W
 
-Headline workload (one "step" = one entry barrier + one fused launch): AllGather+GEMM at the
+Headline workload (one "step" = prepare + one fused launch, i.e. one kernel): AllGather+GEMM at the
 Llama-70B MLP up-projection shape with tensor parallel degree = N: every rank holds an A shard
 [8192/N, 8192] and its column shard of B [8192 -> 3584], and produces C [8192, 3584] (bf16 in,
 fp32 accumulate, bf16 out).  Work per GPU is fixed (481 GFLOP), so scaling is weak.  The same
@@ -340,7 +340,7 @@ def run_ours(args):
                                f"[{Ms},{K}] x B [{K},{N}] -> C [{M},{N}] per GPU",
                    "M": M, "N_per_gpu": N, "K": K, "tp": W,
                    "l2": "operands 246 MB per GPU exceed the 126 MB L2; no flush between steps",
-                   "step": "entry barrier kernel + one fused persistent kernel"},
+                   "step": "one fused persistent kernel (prepare is host-side validation only)"},
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"],
                      "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
                      "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"],
@@ -350,7 +350,7 @@ def run_ours(args):
                      "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH},
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_total / e2e_steps},
-        "gpu_launches": 2 * steps,
+        "gpu_launches": steps,
         "clocks": sampler.summary(),
         "ops": ops_out,
         "plan": plan_summary(_lib, W, rank),
