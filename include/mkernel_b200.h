@@ -142,7 +142,9 @@ int mk_op_status_clear(const mk_symm_view* sync, void* stream);
 /* ---- options (process-wide): "wait_limit_ms" (device wait budget, default 4000),
  *      "n_comm" (dedicated exchange CTAs, -1 = heuristic), "block_n" (0 = heuristic), "group_rows",
  *      "use_nvls" (0/1: exchange through NVSwitch multicast when the buffers have an alias),
- *      "cta_pair" (0/1, default 1: two-SM MMA over CTA pairs when the shape allows). */
+ *      "cta_pair" (0/1, default 1: two-SM MMA over CTA pairs when the shape allows),
+ *      "ar_one_shot" (GEMM+AR: 0 = two-shot, owners reduce and broadcast; 1 = one-shot, every
+ *      rank reduces all rows for itself), "debug_flags" (timing diagnostics; results undefined). */
 int mk_set_option(const char* name, long long value);
 long long mk_get_option(const char* name);
 

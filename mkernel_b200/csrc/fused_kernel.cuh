@@ -126,7 +126,7 @@ __device__ __forceinline__ TileInfo tile_info(const Sched& s, int t) {
 template <int OP>
 __device__ __forceinline__ __nv_bfloat16* output_row(const OpParams& p, int grow) {
   const Sched& s = p.sched;
-  if (OP == OP_RS && s.world > 1) {
+  if (OP == OP_RS && s.world > 1 && !(p.debug_flags & 2)) {
     // ReduceScatter: the row belongs to owner o and goes straight into o's buffer, into the
     // slab reserved for this (producing) rank.  Remote when o != rank: posted NVLink writes.
     int o = grow / s.part_rows;
@@ -466,7 +466,7 @@ __device__ __forceinline__ void reduce_span(const ReduceSpan& sp, int W, uint32_
     } else {
 #pragma unroll
       for (int d = 0; d < WT; ++d)
-        if (d < W) ptx::st_global_v4(sp.dst[d] + v * 16, r);
+        if (d < W && sp.dst[d] != nullptr) ptx::st_global_v4(sp.dst[d] + v * 16, r);
     }
   }
   ptx::cp_async_wait<0>();
@@ -497,7 +497,8 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
   if (W <= 1 || p.n_items <= 0) return;
   wc.where = (blockIdx.x << 8) | 0x10u | (threadIdx.x >> 5);
   const bool nvls_ag = OP == OP_AG && p.use_nvls && p.mc_data != nullptr;
-  const bool nvls_ar = OP == OP_AR && p.use_nvls && p.mc_data != nullptr && p.mc_out != nullptr;
+  const bool nvls_ar = OP == OP_AR && p.use_nvls && !s.one_shot && p.mc_data != nullptr &&
+                       p.mc_out != nullptr;
   const long long row_bytes = (OP == OP_AG ? static_cast<long long>(p.K) : static_cast<long long>(s.N)) * 2;
   char* const local = static_cast<char*>(p.peer_data[s.rank]);
   uint32_t entered_mask = 1u << s.rank;  // ranks known to have entered this launch
@@ -537,7 +538,7 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
         if (!__all_sync(0xffffffffu, ok)) return;
         for (int r = first; r <= last; ++r) entered_mask |= 1u << r;
       }
-      push_span<R>(local + base, dst + base, n_vec, nvls_ag, ring, lane);
+      if (!(p.debug_flags & 1)) push_span<R>(local + base, dst + base, n_vec, nvls_ag, ring, lane);
       __syncwarp();
       if (lane == 0) {
         ptx::fence_acq_rel_sys();
@@ -559,11 +560,28 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
       ready = __shfl_sync(0xffffffffu, ready, 0);
       if (!ready) {
         bool ok = true;
-        for (int idx = lane; idx < W * s.Q && ok; idx += 32) {
-          const int src = idx / s.Q, q = idx % s.Q;
-          const uint32_t* f = p.sync + SW_FLAGS + tile_flag_index(s, src, rb, q);
-          ok = bounded_wait<true>(wc, [&] { return ptx::ld_acquire_sys(f) == epoch; },
-                                  ST_TIMEOUT_TILE, (src << 24) | rb, q);
+        if ((s.Q & 3) == 0) {
+          // The Q flags of one source rank are contiguous: poll them four at a time, all of a
+          // lane's vectors per round (independent loads, one memory latency per round).
+          const int vq = s.Q >> 2, n_v = W * vq;
+          ok = bounded_wait<true>(wc, [&] {
+            bool all = true;
+            for (int idx = lane; idx < n_v; idx += 32) {
+              const int src = idx / vq, q4 = idx % vq;
+              const uint4 v = ptx::ld_relaxed_sys_v4(p.sync + SW_FLAGS +
+                                                     tile_flag_index(s, src, rb, q4 * 4));
+              all = all && v.x == epoch && v.y == epoch && v.z == epoch && v.w == epoch;
+            }
+            return all;
+          }, ST_TIMEOUT_TILE, rb, 0);
+          ptx::fence_acq_rel_sys();
+        } else {
+          for (int idx = lane; idx < W * s.Q && ok; idx += 32) {
+            const int src = idx / s.Q, q = idx % s.Q;
+            const uint32_t* f = p.sync + SW_FLAGS + tile_flag_index(s, src, rb, q);
+            ok = bounded_wait<true>(wc, [&] { return ptx::ld_acquire_sys(f) == epoch; },
+                                    ST_TIMEOUT_TILE, (src << 24) | rb, q);
+          }
         }
         if (!__all_sync(0xffffffffu, ok)) return;
         if (lane == 0) ptx::st_release_gpu(summary, epoch);
@@ -575,7 +593,7 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
       const long long v_begin = static_cast<long long>(c) * p.item_vecs;
       long long n_vec = piece_vecs - v_begin;
       if (n_vec > p.item_vecs) n_vec = p.item_vecs;
-      if (n_vec > 0) {
+      if (n_vec > 0 && !(p.debug_flags & 1)) {
         const long long base = static_cast<long long>(row0) * row_bytes + v_begin * 16;
         if (nvls_ar) {
           reduce_span_nvls(static_cast<const char*>(p.mc_data) + base,
@@ -583,7 +601,7 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
         } else {
           ReduceSpan sp;
           sp.n_vec = n_vec;
-          sp.mc_dst = (OP == OP_AR && p.use_nvls && p.mc_out != nullptr)
+          sp.mc_dst = (OP == OP_AR && p.use_nvls && !s.one_shot && p.mc_out != nullptr)
                           ? static_cast<char*>(p.mc_out) + base : nullptr;
 #pragma unroll
           for (int r = 0; r < kMaxWorld; ++r) {
@@ -594,6 +612,8 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
                             : static_cast<const char*>(p.peer_data[r]) + base;
             sp.dst[r] = r >= W ? nullptr
                         : (OP == OP_RS) ? local + base : static_cast<char*>(p.peer_out[r]) + base;
+            // one-shot AllReduce: every rank reduces every row, for its own output only
+            if (OP == OP_AR && s.one_shot && r < W && r != s.rank) sp.dst[r] = nullptr;
           }
           if (W <= 2) reduce_span<OP, 2, R>(sp, W, ring, lane);
           else if (W <= 4) reduce_span<OP, 4, R>(sp, W, ring, lane);

@@ -15,6 +15,8 @@ struct OpParams {
   int item_vecs;         // RS/AR: 16-byte vectors per exchange work item
   int n_items;           // exchange work items of this rank for this launch
   int use_nvls;          // exchange through NVSwitch multicast addresses when available
+  int debug_flags;       // timing diagnostics only (results undefined): 1 = exchange workers skip
+                         // the data movement but keep the protocol, 2 = RS epilogue stores locally
   uint32_t epoch_arg;    // GEMM+AR: caller-provided epoch; other ops read SW_EPOCH
   uint64_t wait_limit_ns;
 

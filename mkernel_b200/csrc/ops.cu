@@ -29,6 +29,8 @@ struct Options {
   long long block_n = 0;
   long long group_rows = 0;
   long long use_nvls = 0;
+  long long debug_flags = 0;
+  long long ar_one_shot = 0;  // GEMM+AR: 1 = every rank reduces all rows itself (no broadcast)
   long long cta_pair = 1;   // 1: run compute CTAs as pairs (two-SM MMA) when the shape allows
 };
 static Options g_opt;
@@ -42,6 +44,8 @@ static long long* option_slot(const char* name) {
   if (!strcmp(name, "group_rows")) return &g_opt.group_rows;
   if (!strcmp(name, "use_nvls")) return &g_opt.use_nvls;
   if (!strcmp(name, "cta_pair")) return &g_opt.cta_pair;
+  if (!strcmp(name, "debug_flags")) return &g_opt.debug_flags;
+  if (!strcmp(name, "ar_one_shot")) return &g_opt.ar_one_shot;
   return nullptr;
 }
 
@@ -105,6 +109,10 @@ static int make_plan(int op, int rank, int world, int M, int N, int K, int b_lay
   if (group <= 0) group = 8;
   Plan pl;
   pl.sched = make_sched(op, rank, world, M, N, bn, group);
+  if (op == OP_AR && world > 1 && o.ar_one_shot != 0) {
+    pl.sched.one_shot = 1;
+    pl.sched.interleave = 0;
+  }
   pl.K = K;
   pl.k_blocks = ceil_div(K, kBlockK);
   pl.b_mn_major = b_layout == MK_B_KN ? 1 : 0;
@@ -262,6 +270,7 @@ static int run_op(const OpArgs& a, cudaStream_t stream) {
   {
     std::lock_guard<std::mutex> g(g_opt_mu);
     want_nvls = g_opt.use_nvls != 0;
+    p.debug_flags = (int)g_opt.debug_flags;
   }
   if (a.world > 1 && a.op != OP_GEMM) {
     const int workers = (pl.grid - pl.n_comm) + 8 * pl.n_comm;

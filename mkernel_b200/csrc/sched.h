@@ -71,6 +71,7 @@ struct Sched {
   int Q;           // column blocks: ceil(N / block_n)
   int group_rows;  // raster group height in row-blocks
   int interleave;  // RS/AR: 1 when part_rows % 128 == 0 (owner-interleaved order)
+  int one_shot;    // AR only: every rank reduces every row for itself (no result broadcast)
 };
 
 MKB_HD int ceil_div(int a, int b) { return (a + b - 1) / b; }
@@ -88,6 +89,7 @@ MKB_HD Sched make_sched(int op, int rank, int world, int M, int N, int block_n, 
   s.group_rows = group_rows < 1 ? 1 : group_rows;
   s.interleave = ((op == OP_RS || op == OP_AR) && world > 1 && (s.part_rows % kBlockM) == 0 &&
                   s.part_blocks * world == s.P) ? 1 : 0;
+  s.one_shot = 0;
   return s;
 }
 
@@ -136,6 +138,7 @@ MKB_HD int rowblock_shard(const Sched& s, int rb) { return rb / s.part_blocks; }
 
 // RS/AR: owners whose row range [o*part_rows, (o+1)*part_rows) intersects row-block rb.
 MKB_HD void rowblock_owners(const Sched& s, int rb, int* lo, int* hi) {
+  if (s.one_shot) { *lo = 0; *hi = s.world - 1; return; }
   const int r0 = rb * kBlockM;
   int r1 = r0 + kBlockM; if (r1 > s.M) r1 = s.M;
   *lo = r0 / s.part_rows;
@@ -145,8 +148,11 @@ MKB_HD void rowblock_owners(const Sched& s, int rb, int* lo, int* hi) {
 
 // RS/AR reduce items of owner `o`: item k is the intersection of the owner's rows with
 // row-block (first_block + k).
-MKB_HD int owner_first_block(const Sched& s, int o) { return (o * s.part_rows) / kBlockM; }
+MKB_HD int owner_first_block(const Sched& s, int o) {
+  return s.one_shot ? 0 : (o * s.part_rows) / kBlockM;
+}
 MKB_HD int owner_num_items(const Sched& s, int o) {
+  if (s.one_shot) return s.P;
   int r0 = o * s.part_rows, r1 = r0 + s.part_rows;
   if (r1 > s.M) r1 = s.M;
   if (r1 <= r0) return 0;
@@ -155,6 +161,7 @@ MKB_HD int owner_num_items(const Sched& s, int o) {
 MKB_HD void owner_item_rows(const Sched& s, int o, int k, int* row0, int* row1) {
   const int rb = owner_first_block(s, o) + k;
   int a = rb * kBlockM, b = a + kBlockM;
+  if (s.one_shot) { *row0 = a; *row1 = b > s.M ? s.M : b; return; }
   const int r0 = o * s.part_rows;
   int r1 = r0 + s.part_rows; if (r1 > s.M) r1 = s.M;
   if (a < r0) a = r0;
@@ -185,7 +192,7 @@ MKB_HD int gather_num_items(const Sched& s, int nvls) {
   return (nvls ? 1 : s.world - 1) * s.part_blocks * kGatherSub;
 }
 MKB_HD int reduce_chunks_per_piece(const Sched& s, int item_vecs) {
-  int rows = s.part_rows < kBlockM ? s.part_rows : kBlockM;
+  int rows = (s.part_rows < kBlockM && !s.one_shot) ? s.part_rows : kBlockM;
   long long vecs = (long long)rows * s.N / 8;
   return (int)((vecs + item_vecs - 1) / item_vecs);
 }
@@ -193,7 +200,7 @@ MKB_HD int reduce_num_items(const Sched& s, int owner, int item_vecs) {
   return owner_num_items(s, owner) * reduce_chunks_per_piece(s, item_vecs);
 }
 MKB_HD int choose_item_vecs(const Sched& s, int workers) {
-  long long total = (long long)s.part_rows * s.N / 8;
+  long long total = (long long)(s.one_shot ? s.M : s.part_rows) * s.N / 8;
   long long v = total / (2LL * (workers > 0 ? workers : 1));
   if (v < 128) v = 128;
   if (v > 4096) v = 4096;
