@@ -98,15 +98,38 @@ static int make_plan(int op, int rank, int world, int M, int N, int K, int b_lay
   if (n_comm > num_sms - 1) n_comm = num_sms - 1;
   const int n_comp_max = num_sms - n_comm;
 
-  const int quantum = b_layout == MK_B_KN ? 64 : 32;
   int m_blocks = op == OP_AG ? world * ceil_div(M / world, kBlockM) : ceil_div(M, kBlockM);
+  // CTA pairs (two-SM MMA) need an even number of row-blocks and pay off only when the GEMM
+  // fills the machine; halves that are not multiples of 64 columns run the tensor pipe poorly,
+  // so pair mode picks the tile width among multiples of 128.
+  const bool pair_ok = o.cta_pair != 0 && m_blocks % 2 == 0 && n_comm % 2 == 0 && n_comp_max >= 2 &&
+                       (long long)m_blocks * ceil_div(N, 128) >= n_comp_max;
+  const int quantum = pair_ok ? 128 : (b_layout == MK_B_KN ? 64 : 32);
   int bn = (int)o.block_n;
   if (bn <= 0) bn = choose_block_n(m_blocks, N, n_comp_max, quantum);
-  if (bn < 32 || bn > 256 || bn % quantum != 0)
-    return set_error(MK_ERR_INVALID, "block_n=%d must be a multiple of %d in [32,256]", bn, quantum);
+  const int min_q = b_layout == MK_B_KN ? 64 : 32;
+  if (bn < 32 || bn > 256 || bn % min_q != 0)
+    return set_error(MK_ERR_INVALID, "block_n=%d must be a multiple of %d in [32,256]", bn, min_q);
 
+  // Raster group height: tiles are visited in groups of `group` row-blocks, row-block fastest,
+  // so a group's A rows (group x 128 x K) stay in L2 while B streams past once per group.
+  // Measured on B200: ~16-30 MB of A per group is best (8 row-blocks at K=8192, 32 at K=3584).
   int group = (int)o.group_rows;
-  if (group <= 0) group = 8;
+  if (group <= 0) {
+    const long long rb_bytes = (long long)kBlockM * K * 2;
+    long long g = (24LL << 20) / (rb_bytes > 0 ? rb_bytes : 1);
+    g &= ~1LL;
+    if (g < 2) g = 2;
+    if (g > 64) g = 64;
+    if (op == OP_AG && world > 1) {
+      // do not let the first groups reach into shards that have not arrived yet
+      int pb = ceil_div(M / world, kBlockM);
+      if (pb >= 2) pb &= ~1;
+      if (g > pb) g = pb;
+    }
+    if ((op == OP_RS || op == OP_AR) && world > 1 && g >= world) g = g / world * world;
+    group = (int)g;
+  }
   Plan pl;
   pl.sched = make_sched(op, rank, world, M, N, bn, group);
   if (op == OP_AR && world > 1 && o.ar_one_shot != 0) {
@@ -122,8 +145,8 @@ static int make_plan(int op, int rank, int world, int M, int N, int K, int b_lay
   // CTA pairs: consecutive tiles (2i, 2i+1) must share a column block, which holds when every
   // raster group has an even number of row-blocks; the pair splits B's rows in two halves.
   pl.cg = 1;
-  if (o.cta_pair != 0 && pl.sched.P % 2 == 0 && pl.sched.group_rows % 2 == 0 && tiles >= 2 &&
-      bn % (pl.b_mn_major ? 128 : 32) == 0 && n_comm % 2 == 0 && (n_comp & ~1) >= 2) {
+  if (pair_ok && pl.sched.P % 2 == 0 && pl.sched.group_rows % 2 == 0 && tiles >= 2 &&
+      bn % (pl.b_mn_major ? 128 : 32) == 0 && (n_comp & ~1) >= 2) {
     pl.cg = 2;
     n_comp &= ~1;
   }

@@ -201,7 +201,9 @@ MKB_HD int reduce_num_items(const Sched& s, int owner, int item_vecs) {
 }
 MKB_HD int choose_item_vecs(const Sched& s, int workers) {
   long long total = (long long)(s.one_shot ? s.M : s.part_rows) * s.N / 8;
-  long long v = total / (2LL * (workers > 0 ? workers : 1));
+  // one item per worker when the whole exchange is small (a single round trip of latency),
+  // capped so that large exchanges still balance and follow the GEMM's progress
+  long long v = (total + (workers > 0 ? workers : 1) - 1) / (workers > 0 ? workers : 1);
   if (v < 128) v = 128;
   if (v > 4096) v = 4096;
   return (int)((v + 31) / 32 * 32);

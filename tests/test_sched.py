@@ -95,11 +95,17 @@ def test_owner_items_partition_the_rows(op, world, M, N):
 
 
 def test_block_width_avoids_wave_quantisation():
-    # 8192 x 3584 on 148 CTAs: 256-wide tiles need 7 waves for 6.05 waves of work
-    p = _lib.plan_op(OP_GEMM, 0, 1, 8192, 3584, 8192, 0, 148)
+    # 8192 x 3584 on 148 independent CTAs: 256-wide tiles need 7 waves for 6.05 waves of work,
+    # so the planner narrows the tiles (CTA pairs keep 256: narrower halves run the MMA poorly)
+    _lib.set_option("cta_pair", 0)
+    try:
+        p = _lib.plan_op(OP_GEMM, 0, 1, 8192, 3584, 8192, 0, 148)
+    finally:
+        _lib.set_option("cta_pair", 1)
     tiles = p.row_blocks * p.col_blocks
     waves = -(-tiles // p.grid)
     assert tiles / (waves * p.grid) > 0.95
+    assert _lib.plan_op(OP_GEMM, 0, 1, 8192, 3584, 8192, 0, 148).block_n % 128 == 0
     # decode-shaped all-reduce: every tile gets its own CTA
     p = _lib.plan_op(OP_AR, 0, 8, 128, 8192, 1024, 1, 148)
     assert p.row_blocks * p.col_blocks <= p.grid - p.n_comm
