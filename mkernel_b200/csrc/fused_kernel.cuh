@@ -436,13 +436,12 @@ __device__ __forceinline__ void reduce_span(const ReduceSpan& sp, int W, uint32_
   auto slot = [&](long long i, int src) {
     return ring + ((static_cast<uint32_t>(i % DC) * WT + src) * 32u + lane) * 16u;
   };
-  const uint64_t pol = ptx::l2_evict_first_policy();   // partials are read exactly once
   auto issue = [&](long long i) {
     if (i < n_mine) {
       const long long v = vec_of(i);
 #pragma unroll
       for (int src = 0; src < WT; ++src)
-        if (src < W) ptx::cp_async_16_stream(slot(i, src), sp.src[src] + v * 16, pol);
+        if (src < W) ptx::cp_async_16(slot(i, src), sp.src[src] + v * 16);
     }
     ptx::cp_async_commit();
   };
