@@ -113,22 +113,19 @@ static int make_plan(int op, int rank, int world, int M, int N, int K, int b_lay
 
   // Raster group height: tiles are visited in groups of `group` row-blocks, row-block fastest,
   // so a group's A rows (group x 128 x K) stay in L2 while B streams past once per group.
-  // Measured on B200: ~16-30 MB of A per group is best (8 row-blocks at K=8192, 32 at K=3584).
+  // One GPU: ~16-30 MB of A per group measured best (8 row-blocks at K=8192, up to 32 at
+  // K=3584).  With an exchange running, 8 (one shard / one owner round at W=8) measured best.
   int group = (int)o.group_rows;
   if (group <= 0) {
-    const long long rb_bytes = (long long)kBlockM * K * 2;
-    long long g = (24LL << 20) / (rb_bytes > 0 ? rb_bytes : 1);
-    g &= ~1LL;
-    if (g < 2) g = 2;
-    if (g > 64) g = 64;
-    if (op == OP_AG && world > 1) {
-      // do not let the first groups reach into shards that have not arrived yet
-      int pb = ceil_div(M / world, kBlockM);
-      if (pb >= 2) pb &= ~1;
-      if (g > pb) g = pb;
+    group = 8;
+    if (world == 1) {
+      const long long rb_bytes = (long long)kBlockM * K * 2;
+      long long g = (24LL << 20) / (rb_bytes > 0 ? rb_bytes : 1);
+      g &= ~1LL;
+      if (g < 8) g = 8;
+      if (g > 32) g = 32;
+      group = (int)g;
     }
-    if ((op == OP_RS || op == OP_AR) && world > 1 && g >= world) g = g / world * world;
-    group = (int)g;
   }
   Plan pl;
   pl.sched = make_sched(op, rank, world, M, N, bn, group);
@@ -166,8 +163,32 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
+// Encoding a descriptor costs a few microseconds of host time, which matters for the
+// latency-bound shapes; the last few descriptors are kept per thread, keyed by all inputs.
+struct MapKey {
+  const void* base;
+  uint64_t inner, outer, ld;
+  uint32_t box_inner, box_outer;
+  bool operator==(const MapKey& o) const {
+    return base == o.base && inner == o.inner && outer == o.outer && ld == o.ld &&
+           box_inner == o.box_inner && box_outer == o.box_outer;
+  }
+};
+struct MapCache {
+  static constexpr int kSlots = 16;
+  MapKey key[kSlots];
+  CUtensorMap map[kSlots];
+  bool used[kSlots] = {};
+  int next = 0;
+};
+
 static int encode_2d_bf16(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer,
                           uint64_t ld_elems, uint32_t box_inner, uint32_t box_outer) {
+  static thread_local MapCache cache;
+  const MapKey k{base, inner, outer, ld_elems, box_inner, box_outer};
+  for (int i = 0; i < MapCache::kSlots; ++i) {
+    if (cache.used[i] && cache.key[i] == k) { *map = cache.map[i]; return MK_OK; }
+  }
   static EncodeTiledFn fn = nullptr;
   if (!fn) {
     void* p = nullptr;
@@ -186,6 +207,10 @@ static int encode_2d_bf16(CUtensorMap* map, const void* base, uint64_t inner, ui
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return set_error(MK_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  cache.key[cache.next] = k;
+  cache.map[cache.next] = *map;
+  cache.used[cache.next] = true;
+  cache.next = (cache.next + 1) % MapCache::kSlots;
   return MK_OK;
 }
 
