@@ -24,6 +24,28 @@ def _stream() -> ctypes.c_void_p:
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
+class _on_device:
+    """Make `index` the current CUDA device for the duration of a call; free when it already is
+    (the common case: one process per GPU), since these wrappers sit on latency-bound paths."""
+
+    __slots__ = ("index", "prev")
+
+    def __init__(self, index):
+        self.index = index.index if isinstance(index, torch.device) else int(index)
+        self.prev = None
+
+    def __enter__(self):
+        cur = torch.cuda.current_device()
+        if cur != self.index:
+            self.prev = cur
+            torch.cuda.set_device(self.index)
+
+    def __exit__(self, *exc):
+        if self.prev is not None:
+            torch.cuda.set_device(self.prev)
+        return False
+
+
 def _require(cond: bool, msg: str) -> None:
     if not cond:
         raise RuntimeError(msg)
@@ -45,7 +67,7 @@ def gemm_bf16(A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, b_layout: int =
     kb = B.shape[1] if b_layout == _lib.MK_B_NK else B.shape[0]
     _require(kb == K, f"A and B disagree on K: {K} vs {kb}")
     _require(tuple(C.shape) == (M, N), f"C must be [{M},{N}]")
-    with torch.cuda.device(A.device):
+    with _on_device(A.device):
         _lib.check(_lib.lib().mk_gemm_bf16(A.data_ptr(), B.data_ptr(), C.data_ptr(), M, N, K,
                                            b_layout, status.data_ptr() if status is not None else None,
                                            _stream()))
@@ -54,7 +76,7 @@ def gemm_bf16(A: torch.Tensor, B: torch.Tensor, C: torch.Tensor, b_layout: int =
 def ag_gemm_warp_specialized_prepare(A_copy_ready: DistBuffer, M: int = 0, N: int = 0) -> None:
     """All-rank entry barrier + epoch bump on the current stream (M, N kept for compatibility)."""
     _require(isinstance(A_copy_ready, DistBuffer), "A_copy_ready must be a DistBuffer")
-    with torch.cuda.device(A_copy_ready.local_rank_):
+    with _on_device(A_copy_ready.local_rank_):
         _lib.check(_lib.lib().mk_ag_gemm_prepare(A_copy_ready.view_ref(), _stream()))
 
 
@@ -73,7 +95,7 @@ def ag_gemm_warp_specialized_launch(A: DistBuffer, A_copy_ready: DistBuffer, B: 
     N = B.size(0)
     _require(B.size(1) == K, f"B must be [N, K] with K={K}")
     _require(tuple(C.shape) == (W, Ms, N), f"C must be [{W},{Ms},{N}]")
-    with torch.cuda.device(A.local_rank_):
+    with _on_device(A.local_rank_):
         _lib.check(_lib.lib().mk_ag_gemm_launch(A.view_ref(), A_copy_ready.view_ref(),
                                                 B.data_ptr(), C.data_ptr(), W * Ms, N, K,
                                                 _stream()))
@@ -82,7 +104,7 @@ def ag_gemm_warp_specialized_launch(A: DistBuffer, A_copy_ready: DistBuffer, B: 
 def gemm_rs_blackwell_prepare(A, B, C: DistBuffer, sync: DistBuffer) -> None:
     """Zero the synchronisation words once; the caller then synchronises and barriers."""
     _require(isinstance(sync, DistBuffer), "sync must be a DistBuffer")
-    with torch.cuda.device(sync.local_rank_):
+    with _on_device(sync.local_rank_):
         _lib.check(_lib.lib().mk_gemm_rs_prepare(sync.view_ref(), _stream()))
 
 
@@ -97,7 +119,7 @@ def gemm_rs_blackwell_launch(A: torch.Tensor, B: torch.Tensor, C: DistBuffer,
     N = B.size(0)
     _require(B.size(1) == K, f"B must be [N, K] with K={K}")
     _require(C.dtype == torch.bfloat16 and tuple(C.shape) == (M, N), f"C must be bf16 [{M},{N}]")
-    with torch.cuda.device(C.local_rank_):
+    with _on_device(C.local_rank_):
         _lib.check(_lib.lib().mk_gemm_rs_launch(A.data_ptr(), B.data_ptr(), C.view_ref(),
                                                 sync.view_ref(), M, N, K, _stream()))
 
@@ -120,7 +142,7 @@ def gemm_ar_intranode_blackwell(A: torch.Tensor, B: torch.Tensor, C: DistBuffer,
     for d, n in ((C, "C"), (C_final, "C_final")):
         _require(d.dtype == torch.bfloat16 and tuple(d.shape) == (M, N), f"{n} must be bf16 [{M},{N}]")
     _require(int(epoch) >= 1, "epoch starts at 1 and must increase by one per call")
-    with torch.cuda.device(C.local_rank_):
+    with _on_device(C.local_rank_):
         _lib.check(_lib.lib().mk_gemm_ar_launch(A.data_ptr(), B.data_ptr(), C.view_ref(),
                                                 barrier.view_ref(), C_final.view_ref(), M, N, K,
                                                 int(epoch), b_layout, _stream()))
@@ -130,11 +152,11 @@ def op_status(sync: DistBuffer) -> tuple[int, int, int, int]:
     """Status words of an operator's synchronisation buffer; raises MkError if a device wait
     expired.  Synchronises the device."""
     out = (ctypes.c_uint32 * 4)()
-    with torch.cuda.device(sync.local_rank_):
+    with _on_device(sync.local_rank_):
         _lib.check(_lib.lib().mk_op_status(sync.view_ref(), out))
     return tuple(int(x) for x in out)
 
 
 def op_status_clear(sync: DistBuffer) -> None:
-    with torch.cuda.device(sync.local_rank_):
+    with _on_device(sync.local_rank_):
         _lib.check(_lib.lib().mk_op_status_clear(sync.view_ref(), _stream()))
