@@ -242,8 +242,11 @@ MKB_HD int choose_block_n(int M_blocks, int N, int n_compute_ctas, int quantum) 
     const int q = ceil_div(N, bn);
     const long long tiles = (long long)M_blocks * q;
     const long long waves = (tiles + n_compute_ctas - 1) / n_compute_ctas;
-    // fixed per-tile overhead (epilogue hand-off, pipeline refill) ~ 24 columns' worth of MMA time
-    const long long cost = waves * (bn + 24);
+    // fixed per-tile overhead (epilogue hand-off, pipeline refill) ~ 24 columns' worth of MMA
+    // time; narrower tiles also re-read A more often per output column and run the MMA below
+    // its shared-memory-bound rate (measured per-column slowdown: ~1.1x at 192, ~1.35x at 128)
+    const long long eff = bn >= 224 ? 100 : bn >= 192 ? 110 : bn >= 128 ? 135 : 160;
+    const long long cost = waves * (bn + 24) * eff;
     if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
   }
   return best;
