@@ -100,6 +100,13 @@ int mk_ag_gemm_prepare(const mk_symm_view* ready, void* stream);
 int mk_ag_gemm_launch(const mk_symm_view* A, const mk_symm_view* ready, const void* B, void* C,
                       int M, int N, int K, void* stream);
 
+/* Same with B in either layout and an optional caller-supplied epoch (0 = device epoch; otherwise
+ * strictly increasing per launch on this `ready` buffer).  Replaces the shape of
+ * ag_gemm_multinode (include/operators/ag_gemm/session.cuh:210-229), whose B is [K, N] and whose
+ * epoch comes from the host, for a single node. */
+int mk_ag_gemm_launch_ex(const mk_symm_view* A, const mk_symm_view* ready, const void* B, void* C,
+                         int M, int N, int K, int b_layout, uint32_t epoch, void* stream);
+
 /* GEMM + ReduceScatter.  Replaces gemm_rs_blackwell_prepare / _launch
  * (src/gemm_rs_blackwell.cu:642-732).  A: [M, K_local], B: [N, K_local], C: symmetric [M, N]
  * (workspace: rank s's partial rows of owner o land in slab s of o's copy; after the launch rows
@@ -108,6 +115,13 @@ int mk_ag_gemm_launch(const mk_symm_view* A, const mk_symm_view* ready, const vo
 int mk_gemm_rs_prepare(const mk_symm_view* sync, void* stream);
 int mk_gemm_rs_launch(const void* A, const void* B, const mk_symm_view* C,
                       const mk_symm_view* sync, int M, int N, int K, void* stream);
+
+/* Same with B in either layout and an optional caller-supplied epoch (0 = device epoch).
+ * Replaces the shape of gemm_rs_fused (include/operators/gemm_rs/session.cuh:128-153) for a
+ * single node. */
+int mk_gemm_rs_launch_ex(const void* A, const void* B, const mk_symm_view* C,
+                         const mk_symm_view* sync, int M, int N, int K, int b_layout,
+                         uint32_t epoch, void* stream);
 
 /* One-GPU GEMM + ReduceScatter that allocates nothing: C[M,N] = A[M,K] * B[N,K]^T with the
  * kernel's synchronisation words held in a 64 KiB device array built into the library, for

@@ -78,6 +78,10 @@ _SIGNATURES = {
     "mk_ag_gemm_prepare": (c_int, [POINTER(SymmView), c_void_p]),
     "mk_ag_gemm_launch": (c_int, [POINTER(SymmView), POINTER(SymmView), c_void_p, c_void_p,
                                   c_int, c_int, c_int, c_void_p]),
+    "mk_ag_gemm_launch_ex": (c_int, [POINTER(SymmView), POINTER(SymmView), c_void_p, c_void_p,
+                                     c_int, c_int, c_int, c_int, c_uint32, c_void_p]),
+    "mk_gemm_rs_launch_ex": (c_int, [c_void_p, c_void_p, POINTER(SymmView), POINTER(SymmView),
+                                     c_int, c_int, c_int, c_int, c_uint32, c_void_p]),
     "mk_gemm_rs_prepare": (c_int, [POINTER(SymmView), c_void_p]),
     "mk_gemm_rs_launch": (c_int, [c_void_p, c_void_p, POINTER(SymmView), POINTER(SymmView),
                                   c_int, c_int, c_int, c_void_p]),

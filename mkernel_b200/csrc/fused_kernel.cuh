@@ -670,7 +670,9 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
   if (threadIdx.x == 0) {
     *s_abort = 0u;
     uint32_t e = p.epoch_arg;
-    if (p.sync != nullptr && (OP == OP_AG || OP == OP_RS))
+    // AG / RS: the epoch lives on the device (graph replays need no host state) unless the
+    // caller supplies one (the multi-node style signatures pass a host epoch)
+    if (p.sync != nullptr && (OP == OP_AG || OP == OP_RS) && e == 0u)
       e = ptx::ld_relaxed_sys(p.sync + SW_EPOCH) + 1u;
     *s_epoch = e;
     if (!is_comm) {

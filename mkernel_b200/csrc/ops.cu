@@ -454,7 +454,14 @@ int mk_ag_gemm_prepare(const mk_symm_view* ready, void* stream) {
 
 int mk_ag_gemm_launch(const mk_symm_view* A, const mk_symm_view* ready, const void* B, void* C,
                       int M, int N, int K, void* stream) {
+  return mk_ag_gemm_launch_ex(A, ready, B, C, M, N, K, MK_B_NK, 0, stream);
+}
+
+int mk_ag_gemm_launch_ex(const mk_symm_view* A, const mk_symm_view* ready, const void* B, void* C,
+                         int M, int N, int K, int b_layout, uint32_t epoch, void* stream) {
   if (!B || !C) return set_error(MK_ERR_INVALID, "mk_ag_gemm_launch: null operand");
+  if (b_layout != MK_B_KN && b_layout != MK_B_NK)
+    return set_error(MK_ERR_INVALID, "mk_ag_gemm_launch: unknown B layout %d", b_layout);
   if (M < 1 || K < 1) return set_error(MK_ERR_INVALID, "mk_ag_gemm_launch: bad shape");
   int rc = check_view(A, "A", (size_t)M * K * 2);
   if (rc != MK_OK) return rc;
@@ -465,8 +472,8 @@ int mk_ag_gemm_launch(const mk_symm_view* A, const mk_symm_view* ready, const vo
   OpArgs a;
   memset(&a, 0, sizeof(a));
   a.op = OP_AG; a.A = A->peer[A->rank]; a.a_rows = M; a.B = B; a.C = C;
-  a.M = M; a.N = N; a.K = K; a.b_layout = MK_B_NK; a.rank = A->rank; a.world = A->world;
-  a.sync = ready; a.data = A;
+  a.M = M; a.N = N; a.K = K; a.b_layout = b_layout; a.rank = A->rank; a.world = A->world;
+  a.sync = ready; a.data = A; a.epoch = epoch;
   return run_op(a, static_cast<cudaStream_t>(stream));
 }
 
@@ -479,7 +486,15 @@ int mk_gemm_rs_prepare(const mk_symm_view* sync, void* stream) {
 
 int mk_gemm_rs_launch(const void* A, const void* B, const mk_symm_view* C,
                       const mk_symm_view* sync, int M, int N, int K, void* stream) {
+  return mk_gemm_rs_launch_ex(A, B, C, sync, M, N, K, MK_B_NK, 0, stream);
+}
+
+int mk_gemm_rs_launch_ex(const void* A, const void* B, const mk_symm_view* C,
+                         const mk_symm_view* sync, int M, int N, int K, int b_layout,
+                         uint32_t epoch, void* stream) {
   if (!A || !B) return set_error(MK_ERR_INVALID, "mk_gemm_rs_launch: null operand");
+  if (b_layout != MK_B_KN && b_layout != MK_B_NK)
+    return set_error(MK_ERR_INVALID, "mk_gemm_rs_launch: unknown B layout %d", b_layout);
   if (M < 1 || N < 1) return set_error(MK_ERR_INVALID, "mk_gemm_rs_launch: bad shape");
   int rc = check_view(C, "C", (size_t)M * N * 2);
   if (rc != MK_OK) return rc;
@@ -490,8 +505,8 @@ int mk_gemm_rs_launch(const void* A, const void* B, const mk_symm_view* C,
   OpArgs a;
   memset(&a, 0, sizeof(a));
   a.op = OP_RS; a.A = A; a.a_rows = M; a.B = B; a.C = C->peer[C->rank];
-  a.M = M; a.N = N; a.K = K; a.b_layout = MK_B_NK; a.rank = C->rank; a.world = C->world;
-  a.sync = sync; a.data = C;
+  a.M = M; a.N = N; a.K = K; a.b_layout = b_layout; a.rank = C->rank; a.world = C->world;
+  a.sync = sync; a.data = C; a.epoch = epoch;
   return run_op(a, static_cast<cudaStream_t>(stream));
 }
 

@@ -10,7 +10,7 @@ from __future__ import annotations
 import sys
 import types
 
-from . import _lib, ops
+from . import _lib, multinode_compat, ops
 from .dist_buffer import DistBuffer
 
 _EXPORTS = {
@@ -37,14 +37,20 @@ def load(name: str) -> types.ModuleType:
     Raises RuntimeError if the name is not an operator of this library or the native library
     has not been built (same failure mode as the reference when the .so is absent).
     """
-    if name not in _EXPORTS:
-        raise RuntimeError(f"unknown kernel module '{name}'; available: {sorted(_EXPORTS)}")
+    if name not in _EXPORTS and name not in multinode_compat.EXPORTS:
+        raise RuntimeError(f"unknown kernel module '{name}'; available: "
+                           f"{sorted(list(_EXPORTS) + list(multinode_compat.EXPORTS))}")
     _lib.lib()  # fail loudly now if the native library is missing
     mod_name = f"mkernel_release_{name}"
     mod = types.ModuleType(mod_name, f"B200-native stand-in for build/lib{name}.so")
     mod.DistBuffer = DistBuffer
-    for attr in _EXPORTS[name]:
-        setattr(mod, attr, getattr(ops, attr))
+    if name in _EXPORTS:
+        for attr in _EXPORTS[name]:
+            setattr(mod, attr, getattr(ops, attr))
+    else:
+        # multi-node style signatures of the same operators, served on one node
+        for attr in multinode_compat.EXPORTS[name]:
+            setattr(mod, attr, getattr(multinode_compat, attr))
     if name == "gemm_rs_blackwell":
         mod.gemm_rs_blackwell_world_size = _lib.MK_MAX_WORLD
     mod.op_status = ops.op_status

@@ -157,7 +157,90 @@ def case_ar(rank, world, M, N, K, seed, iters, max_rows, layout=_lib.MK_B_KN, mu
     return res
 
 
-CASES = {"ag": case_ag, "rs": case_rs, "ar": case_ar}
+def case_compat(rank, world, M, N, K, seed, iters, max_rows):
+    """The multi-node style signatures (ag_gemm_multinode / gemm_rs_fused / gemm_ar_multinode)
+    served on one node: B is [K, N] and the epoch comes from the caller."""
+    dev = torch.device("cuda", rank)
+    res = dict(op="compat", M=M, N=N, K=K, rel=[], status=[], gathered_exact=[])
+    rows = _sample_rows(M, max_rows, seed)
+    # --- AllGather + GEMM
+    ag = mkernel_b200.load("ag_gemm")
+    Ms = M // world
+    shards = [orc.synth_inputs("ag", r, world, M, N, K, seed=seed)[0] for r in range(world)]
+    b_kn = orc.synth_inputs("ag", rank, world, M, N, K, seed=seed)[1]
+    A = ag.DistBuffer((M, K), dtype=torch.bfloat16, local_rank=rank, local_world_size=world,
+                      multicast=True)
+    A.data_.zero_()
+    A.data_[rank * Ms:(rank + 1) * Ms].copy_(shards[rank])
+    barrier = ag.DistBuffer((3, 1024, 1024), dtype=torch.int32, local_rank=rank,
+                            local_world_size=world, multicast=True)
+    barrier.data_.zero_()
+    B = b_kn.contiguous().to(dev)
+    C = torch.zeros((M, N), device=dev, dtype=torch.bfloat16)
+    ag.create_session(0, "127.0.0.1", 0, 0, 0, 0, 0, 0, rank)
+    fifo = ag.get_fifo_handles()
+    sync_all()
+    a_full = torch.cat(shards, 0)
+    ref = a_full[rows].float() @ b_kn.float()
+    for it in range(iters):
+        ag.ag_gemm_multinode(A, B, C, barrier, ag.get_recv_buf_ptr(), *fifo,
+                             ag.get_arrival_flags_ptr(), it + 1, 0, 8, Ms * K * 2, None, 148, 0, 1)
+        torch.cuda.synchronize()
+        res["status"].append(list(ag.op_status(barrier)))
+        res["gathered_exact"].append(bool(torch.equal(A.data_.cpu(), a_full)))
+        res["rel"].append(orc.rel_error(C[rows.to(dev)].cpu(), ref))
+        sync_all()
+    # --- GEMM + ReduceScatter
+    rs = mkernel_b200.load("gemm_rs")
+    rrows = _sample_rows(Ms, max_rows, seed)
+    ref = scale = mine = None
+    for r in range(world):
+        a, b = orc.synth_inputs("rs", r, world, M, N, K, seed=seed + 1)
+        p = a[rank * Ms + rrows].float() @ b.float()
+        ref = p if ref is None else ref + p
+        scale = p.abs() if scale is None else scale + p.abs()
+        if r == rank:
+            mine = (a, b)
+    A2, B2 = mine[0].to(dev), mine[1].contiguous().to(dev)
+    work = rs.DistBuffer((M, N), dtype=torch.bfloat16, local_rank=rank, local_world_size=world)
+    out = rs.DistBuffer((Ms, N), dtype=torch.bfloat16, local_rank=rank, local_world_size=world)
+    bar2 = rs.DistBuffer((2, 1024, 1024), dtype=torch.int32, local_rank=rank, local_world_size=world)
+    bar2.data_.zero_()
+    sync_all()
+    for it in range(iters):
+        rs.gemm_rs_fused(A2, B2, work, out, bar2, None, 0, 0, 0, 0, 0, 0, 0, 0, it + 1, 0, 100, 8,
+                         8, 8, False, 0, None, None, 1)
+        torch.cuda.synchronize()
+        res["status"].append(list(rs.op_status(bar2)))
+        res["rel"].append(orc.rel_error(out.data_[rrows.to(dev)].cpu(), ref, scale))
+        sync_all()
+    # --- GEMM + AllReduce
+    ar = mkernel_b200.load("gemm_ar")
+    ref = scale = mine = None
+    for r in range(world):
+        a, b = orc.synth_inputs("ar", r, world, M, N, K, seed=seed + 2)
+        p = a[rows].float() @ b.float()
+        ref = p if ref is None else ref + p
+        scale = p.abs() if scale is None else scale + p.abs()
+        if r == rank:
+            mine = (a, b)
+    A3, B3 = mine[0].to(dev), mine[1].contiguous().to(dev)
+    C3 = ar.DistBuffer((M, N), dtype=torch.bfloat16, local_rank=rank, local_world_size=world)
+    C3f = ar.DistBuffer((M, N), dtype=torch.bfloat16, local_rank=rank, local_world_size=world)
+    bar3 = ar.DistBuffer((2, 1024, 1024), dtype=torch.int32, local_rank=rank, local_world_size=world)
+    bar3.data_.zero_()
+    sync_all()
+    for it in range(iters):
+        ar.gemm_ar_multinode(A3, B3, C3, bar3, C3f, 0, 0, 0, 0, 0, 0, 0, 0, it + 1, 0, 8, 0, 0, 1,
+                             use_acquire_poll=False)
+        torch.cuda.synchronize()
+        res["status"].append(list(ar.op_status(bar3)))
+        res["rel"].append(orc.rel_error(C3f.data_[rows.to(dev)].cpu(), ref, scale))
+        sync_all()
+    return res
+
+
+CASES = {"ag": case_ag, "rs": case_rs, "ar": case_ar, "compat": case_compat}
 
 
 def run_rank(rank: int, world: int, port: int, key: str, cases: list, out_dir: str, options=None):

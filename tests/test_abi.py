@@ -76,5 +76,10 @@ def test_loader_names():
     assert tuple(mod.gemm_rs_blackwell_sync_shape) == (524288,)
     mod = mkernel_b200.load("gemm_ar_blackwell")
     assert callable(mod.gemm_ar_intranode_blackwell)
+    for name, fn in (("ag_gemm", "ag_gemm_multinode"), ("gemm_rs", "gemm_rs_fused"),
+                     ("gemm_ar", "gemm_ar_multinode")):
+        mod = mkernel_b200.load(name)            # multi-node signatures, served on one node
+        assert callable(getattr(mod, fn)) and callable(mod.create_session)
+        assert mod.get_fifo_handles() == (0, 0, 0, 0, 0)
     with pytest.raises(RuntimeError):
         mkernel_b200.load("ring_attention")

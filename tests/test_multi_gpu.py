@@ -67,6 +67,7 @@ def test_small_shapes_all_ops():
         dict(op="ar", M=128, N=1024, K=256, seed=3, iters=3, max_rows=4096),
         dict(op="ar", M=100, N=264, K=72, seed=3, iters=2, max_rows=4096, layout=0),
         dict(op="ar", M=world * 128, N=512, K=128, seed=3, iters=2, max_rows=4096),
+        dict(op="compat", M=world * 128, N=256, K=192, seed=5, iters=2, max_rows=4096),
     ]
     check(launch(world, cases))
 

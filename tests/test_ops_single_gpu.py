@@ -150,3 +150,48 @@ def test_wait_that_nothing_satisfies_returns_a_status():
     ops.gemm_bf16(A, B, C)
     torch.cuda.synchronize()
     assert orc.rel_error(C.cpu(), (A.float() @ B.float().t()).cpu()) <= orc.REL_TOL
+
+
+def test_multinode_signatures_on_one_gpu():
+    """The multi-node style entry points (B stored [K, N], epoch from the caller, transport
+    arguments ignored) give the same results as the oracle with a world of one."""
+    M, N, K = 256, 192, 320
+    ag = mkernel_b200.load("ag_gemm")
+    a, b_kn = orc.synth_inputs("ag", 0, 1, M, N, K, seed=1)
+    A = ag.DistBuffer((M, K), dtype=torch.bfloat16, local_rank=0, local_world_size=1, multicast=True)
+    A.data_.copy_(a)
+    barrier = ag.DistBuffer((3, 1024, 1024), dtype=torch.int32, local_rank=0, local_world_size=1)
+    barrier.data_.zero_()
+    C = torch.zeros((M, N), device=DEV, dtype=torch.bfloat16)
+    ag.create_session(0, "127.0.0.1", 0, 0, 0, 0, 0, 0, 0)
+    fifo = ag.get_fifo_handles()
+    for epoch in (1, 2):
+        ag.ag_gemm_multinode(A, b_kn.contiguous().to(DEV), C, barrier, ag.get_recv_buf_ptr(), *fifo,
+                             ag.get_arrival_flags_ptr(), epoch, 0, 8, M * K * 2, None, 148, 0, 1)
+        torch.cuda.synchronize()
+        assert orc.rel_error(C.cpu(), orc.ag_gemm_ref([a], b_kn)[1]) <= orc.REL_TOL
+    with pytest.raises(RuntimeError):       # more than one node is not served
+        ag.ag_gemm_multinode(A, b_kn.contiguous().to(DEV), C, barrier, 0, *fifo, 0, 3, 0, 8, 0, None,
+                             148, 0, 2)
+
+    rs = mkernel_b200.load("gemm_rs")
+    a, b_kn = orc.synth_inputs("rs", 0, 1, M, N, K, seed=2)
+    work = rs.DistBuffer((M, N), dtype=torch.bfloat16, local_rank=0, local_world_size=1)
+    out = rs.DistBuffer((M, N), dtype=torch.bfloat16, local_rank=0, local_world_size=1)
+    bar2 = rs.DistBuffer((2, 1024, 1024), dtype=torch.int32, local_rank=0, local_world_size=1)
+    bar2.data_.zero_()
+    rs.gemm_rs_fused(a.to(DEV), b_kn.contiguous().to(DEV), work, out, bar2, None, 0, 0, 0, 0, 0, 0, 0,
+                     0, 1, 0, 100, 8, 8, 8, False, 0, None, None, 1)
+    torch.cuda.synchronize()
+    assert orc.rel_error(out.data_.cpu(), orc.gemm_rs_ref([a], [b_kn])[0]) <= orc.REL_TOL
+
+    ar = mkernel_b200.load("gemm_ar")
+    a, b_kn = orc.synth_inputs("ar", 0, 1, 128, N, K, seed=3)
+    C3 = ar.DistBuffer((128, N), dtype=torch.bfloat16, local_rank=0, local_world_size=1)
+    C3f = ar.DistBuffer((128, N), dtype=torch.bfloat16, local_rank=0, local_world_size=1)
+    bar3 = ar.DistBuffer((2, 1024, 1024), dtype=torch.int32, local_rank=0, local_world_size=1)
+    bar3.data_.zero_()
+    ar.gemm_ar_multinode(a.to(DEV), b_kn.contiguous().to(DEV), C3, bar3, C3f, 0, 0, 0, 0, 0, 0, 0, 0,
+                         1, 0, 8, 0, 0, 1, trace_slot=-1)
+    torch.cuda.synchronize()
+    assert orc.rel_error(C3f.data_.cpu(), orc.gemm_ar_ref([a], [b_kn])[0]) <= orc.REL_TOL
