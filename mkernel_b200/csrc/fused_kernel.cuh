@@ -621,7 +621,8 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
         }
       }
       __syncwarp();
-      if (lane == 0) ptx::fence_acq_rel_sys();   // results (remote for AR) before "item done"
+      // AllReduce: results went to other GPUs; order them before the "item done" count
+      if (OP == OP_AR && lane == 0) ptx::fence_acq_rel_sys();
     }
 
     // 3. AllReduce: the worker that completes the rank's last item tells every rank that this
@@ -721,7 +722,12 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
       exchange_worker<OP, kRingDedicated>(p, smem_base + warp * (kRingDedicated * 32 * 16), wc,
                                           epoch, s_item + warp);
   } else if (warp == 3) {
-    if (OP != OP_GEMM) exchange_worker<OP, kRingInCta>(p, xchg_ring, wc, epoch, s_item + warp);
+    if (OP != OP_GEMM) {
+      if (p.ring_slots == kRingInCtaDeep)
+        exchange_worker<OP, kRingInCtaDeep>(p, xchg_ring, wc, epoch, s_item + warp);
+      else
+        exchange_worker<OP, kRingInCta>(p, xchg_ring, wc, epoch, s_item + warp);
+    }
   } else {
     compute_roles<OP, CG>(&tma_a, &tma_b, p, smem_base, bar_base, epi_stage, *s_tmem, wc, epoch);
   }

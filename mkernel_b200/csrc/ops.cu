@@ -56,6 +56,7 @@ struct Plan {
   Sched sched;
   int K, k_blocks, stages, n_comm, grid, smem;
   int cg;   // 1: independent CTAs; 2: CTA pairs
+  int ring_slots;
   int b_mn_major;
 };
 
@@ -147,8 +148,14 @@ static int make_plan(int op, int rank, int world, int M, int N, int K, int b_lay
     pl.cg = 2;
     n_comp &= ~1;
   }
-  pl.stages = num_stages_cg(bn, pl.cg);
-  pl.smem = smem_bytes_cg(bn, pl.cg);
+  // With an exchange to feed, trade one operand stage for a three times deeper ring of the
+  // in-CTA exchange warp (its throughput is bytes in flight / memory latency) when at least
+  // five stages remain.
+  pl.ring_slots = kRingInCta;
+  if (world > 1 && op != OP_GEMM && num_stages_cg(bn, pl.cg, kRingInCtaDeep) >= 5)
+    pl.ring_slots = kRingInCtaDeep;
+  pl.stages = num_stages_cg(bn, pl.cg, pl.ring_slots);
+  pl.smem = smem_bytes_cg(bn, pl.cg, pl.ring_slots);
   pl.n_comm = n_comm;
   pl.grid = n_comm + n_comp;
   *out = pl;
@@ -314,6 +321,7 @@ static int run_op(const OpArgs& a, cudaStream_t stream) {
   p.stages = pl.stages;
   p.b_mn_major = pl.b_mn_major;
   p.n_comm = pl.n_comm;
+  p.ring_slots = pl.ring_slots;
   bool want_nvls = false;
   {
     std::lock_guard<std::mutex> g(g_opt_mu);

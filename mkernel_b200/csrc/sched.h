@@ -200,10 +200,13 @@ MKB_HD int reduce_num_items(const Sched& s, int owner, int item_vecs) {
   return owner_num_items(s, owner) * reduce_chunks_per_piece(s, item_vecs);
 }
 MKB_HD int choose_item_vecs(const Sched& s, int workers) {
-  long long total = (long long)(s.one_shot ? s.M : s.part_rows) * s.N / 8;
-  // one item per worker when the whole exchange is small (a single round trip of latency),
-  // capped so that large exchanges still balance and follow the GEMM's progress
-  long long v = (total + (workers > 0 ? workers : 1) - 1) / (workers > 0 ? workers : 1);
+  // A row-block's rows become reducible all at once (when its last tile lands on the last
+  // rank), and the final row-block only at the very end of the GEMM: cut one piece (<= 128 rows)
+  // into about one item per worker so that this tail is a single short round for everybody.
+  if (workers < 1) workers = 1;
+  const int rows = (s.part_rows < kBlockM && !s.one_shot) ? s.part_rows : kBlockM;
+  const long long piece = (long long)rows * s.N / 8;
+  long long v = (piece + workers - 1) / workers;
   if (v < 128) v = 128;
   if (v > 4096) v = 4096;
   return (int)((v + 31) / 32 * 32);
@@ -223,13 +226,19 @@ MKB_HD int num_stages(int block_n) {
 MKB_HD int smem_bytes(int block_n) {
   return kSmemFixedBytes + num_stages(block_n) * stage_bytes(block_n);
 }
-MKB_HD int num_stages_cg(int block_n, int cg) {
-  int n = (kSmemBudget - kSmemFixedBytes) / stage_bytes_cg(block_n, cg);
+// `ring_slots` = 16-byte ring slots per lane of the in-CTA exchange warp (32 -> 16 KB, 96 -> 48 KB).
+MKB_HD int smem_fixed_bytes(int ring_slots) {
+  return 1024 + kSmemBarrierBytes + kEpilogueStageBytes + ring_slots * 32 * 16;
+}
+MKB_HD int num_stages_cg(int block_n, int cg, int ring_slots = kRingInCta) {
+  int n = (kSmemBudget - smem_fixed_bytes(ring_slots)) / stage_bytes_cg(block_n, cg);
   return n > kMaxStages ? kMaxStages : n;
 }
-MKB_HD int smem_bytes_cg(int block_n, int cg) {
-  return kSmemFixedBytes + num_stages_cg(block_n, cg) * stage_bytes_cg(block_n, cg);
+MKB_HD int smem_bytes_cg(int block_n, int cg, int ring_slots = kRingInCta) {
+  return smem_fixed_bytes(ring_slots) +
+         num_stages_cg(block_n, cg, ring_slots) * stage_bytes_cg(block_n, cg);
 }
+constexpr int kRingInCtaDeep = 96;     // deeper ring when an operand stage can be given up for it
 
 // Column-block width: pick the multiple of `quantum` in [64, 256] that minimises the number of
 // full waves times the tile width (a proxy for time), preferring wider tiles on ties.
