@@ -397,24 +397,42 @@ __device__ __forceinline__ void accumulate_bf16x8(float (&acc)[8], const uint4& 
 
 // AllGather item: copy `n_vec` 16-byte vectors from the own shard to the same offset of the
 // destination (a peer's buffer or the multicast alias) through the lane-private ring.
+// The ring is used as NS steps of VP vectors per lane; one cp.async commit group per step.
+// The number of groups in flight is kept small (<= 12): with one group per vector and a 96-slot
+// ring (95 groups outstanding) a worker never returned from its wait on this hardware.
 template <int R>
 __device__ __forceinline__ void push_span(const char* src, char* dst, long long n_vec, bool nvls,
                                           uint32_t ring, int lane) {
-  const long long n_mine = n_vec > lane ? (n_vec - 1 - lane) / 32 + 1 : 0;
+  constexpr int VP = R >= 64 ? 8 : 4;   // vectors per lane per step
+  constexpr int NS = R / VP;            // steps in the ring
+  static_assert(NS >= 2 && NS <= 12 && NS * VP == R, "ring geometry");
+  const long long n_mine = n_vec > lane ? (n_vec - 1 - lane) / 32 + 1 : 0;   // vectors of this lane
+  const long long n_steps = (n_mine + VP - 1) / VP;
   auto off = [&](long long e) { return (e * 32 + lane) * 16; };
   auto slot = [&](long long e) { return ring + (static_cast<uint32_t>(e % R) * 32u + lane) * 16u; };
-  for (long long e = 0; e < R - 1; ++e) {
-    if (e < n_mine) ptx::cp_async_16(slot(e), src + off(e));
+  auto issue = [&](long long st) {
+    if (st < n_steps) {
+#pragma unroll
+      for (int j = 0; j < VP; ++j) {
+        const long long e = st * VP + j;
+        if (e < n_mine) ptx::cp_async_16(slot(e), src + off(e));
+      }
+    }
     ptx::cp_async_commit();
-  }
-  for (long long e = 0; e < n_mine; ++e) {
-    const long long nx = e + R - 1;
-    if (nx < n_mine) ptx::cp_async_16(slot(nx), src + off(nx));
-    ptx::cp_async_commit();
-    ptx::cp_async_wait<R - 1>();
-    const uint4 v = ptx::ld_shared_v4(slot(e));
-    if (nvls) ptx::multimem_st_v4(dst + off(e), v);
-    else ptx::st_global_v4(dst + off(e), v);
+  };
+  for (long long st = 0; st < NS - 1; ++st) issue(st);
+  for (long long st = 0; st < n_steps; ++st) {
+    issue(st + NS - 1);
+    ptx::cp_async_wait<NS - 1>();
+#pragma unroll
+    for (int j = 0; j < VP; ++j) {
+      const long long e = st * VP + j;
+      if (e < n_mine) {
+        const uint4 v = ptx::ld_shared_v4(slot(e));
+        if (nvls) ptx::multimem_st_v4(dst + off(e), v);
+        else ptx::st_global_v4(dst + off(e), v);
+      }
+    }
   }
   ptx::cp_async_wait<0>();
 }
@@ -426,47 +444,61 @@ struct ReduceSpan {
   long long n_vec;             // 16-byte vectors in the range
 };
 
-// Reduce item: sum W copies of a range.  Each lane owns every 32nd vector and keeps DC-1 steps
-// (x W copies) of cp.async reads in flight.  fp32 accumulation in fixed rank order 0..W-1.
+// Reduce item: sum W copies of a range.  Each lane owns every 32nd vector; the ring holds NS
+// steps of VP vectors x W copies, one cp.async commit group per step, NS-1 steps in flight.
+// fp32 accumulation in fixed rank order 0..W-1.
 template <int OP, int WT, int R>
 __device__ __forceinline__ void reduce_span(const ReduceSpan& sp, int W, uint32_t ring, int lane) {
-  constexpr int DC = R / WT;
+  constexpr int VP = (R / (WT * 8)) >= 1 ? R / (WT * 8) : 1;   // vectors per lane per step
+  constexpr int NS = R / (WT * VP);                             // steps in the ring
+  static_assert(NS >= 2 && NS <= 12, "ring geometry");
   const long long n_mine = sp.n_vec > lane ? (sp.n_vec - 1 - lane) / 32 + 1 : 0;
-  auto vec_of = [&](long long i) { return i * 32 + lane; };
+  const long long n_steps = (n_mine + VP - 1) / VP;
   auto slot = [&](long long i, int src) {
-    return ring + ((static_cast<uint32_t>(i % DC) * WT + src) * 32u + lane) * 16u;
+    return ring + ((static_cast<uint32_t>(i % (NS * VP)) * WT + src) * 32u + lane) * 16u;
   };
-  auto issue = [&](long long i) {
-    if (i < n_mine) {
-      const long long v = vec_of(i);
+  auto issue = [&](long long st) {
+    if (st < n_steps) {
 #pragma unroll
-      for (int src = 0; src < WT; ++src)
-        if (src < W) ptx::cp_async_16(slot(i, src), sp.src[src] + v * 16);
+      for (int j = 0; j < VP; ++j) {
+        const long long i = st * VP + j;
+        if (i < n_mine) {
+          const long long v = i * 32 + lane;
+#pragma unroll
+          for (int src = 0; src < WT; ++src)
+            if (src < W) ptx::cp_async_16(slot(i, src), sp.src[src] + v * 16);
+        }
+      }
     }
     ptx::cp_async_commit();
   };
-  for (long long i = 0; i < DC - 1; ++i) issue(i);
-  for (long long i = 0; i < n_mine; ++i) {
-    issue(i + DC - 1);
-    ptx::cp_async_wait<DC - 1>();
-    const long long v = vec_of(i);
-    float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+  for (long long st = 0; st < NS - 1; ++st) issue(st);
+  for (long long st = 0; st < n_steps; ++st) {
+    issue(st + NS - 1);
+    ptx::cp_async_wait<NS - 1>();
 #pragma unroll
-    for (int src = 0; src < WT; ++src)
-      if (src < W) accumulate_bf16x8(acc, ptx::ld_shared_v4(slot(i, src)));
-    uint4 r;
-    r.x = ptx::pack_bf16x2(acc[0], acc[1]);
-    r.y = ptx::pack_bf16x2(acc[2], acc[3]);
-    r.z = ptx::pack_bf16x2(acc[4], acc[5]);
-    r.w = ptx::pack_bf16x2(acc[6], acc[7]);
-    if (OP == OP_RS) {
-      ptx::st_global_v4(sp.dst[0] + v * 16, r);
-    } else if (sp.mc_dst != nullptr) {
-      ptx::multimem_st_v4(sp.mc_dst + v * 16, r);
-    } else {
+    for (int j = 0; j < VP; ++j) {
+      const long long i = st * VP + j;
+      if (i >= n_mine) continue;
+      const long long v = i * 32 + lane;
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int d = 0; d < WT; ++d)
-        if (d < W && sp.dst[d] != nullptr) ptx::st_global_v4(sp.dst[d] + v * 16, r);
+      for (int src = 0; src < WT; ++src)
+        if (src < W) accumulate_bf16x8(acc, ptx::ld_shared_v4(slot(i, src)));
+      uint4 r;
+      r.x = ptx::pack_bf16x2(acc[0], acc[1]);
+      r.y = ptx::pack_bf16x2(acc[2], acc[3]);
+      r.z = ptx::pack_bf16x2(acc[4], acc[5]);
+      r.w = ptx::pack_bf16x2(acc[6], acc[7]);
+      if (OP == OP_RS) {
+        ptx::st_global_v4(sp.dst[0] + v * 16, r);
+      } else if (sp.mc_dst != nullptr) {
+        ptx::multimem_st_v4(sp.mc_dst + v * 16, r);
+      } else {
+#pragma unroll
+        for (int d = 0; d < WT; ++d)
+          if (d < W && sp.dst[d] != nullptr) ptx::st_global_v4(sp.dst[d] + v * 16, r);
+      }
     }
   }
   ptx::cp_async_wait<0>();
