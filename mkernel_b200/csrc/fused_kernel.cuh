@@ -681,13 +681,18 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
   extern __shared__ uint8_t smem_raw[];
   const Sched& s = p.sched;
   const int warp = threadIdx.x >> 5;
-  const uint32_t smem_base = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  // Shared-memory layout (1024-byte aligned): [barriers + control words, 1 KB][operand stages]
+  // [epilogue transpose buffers, 16 KB][ring of the in-CTA exchange warp].  The control block
+  // comes first so that no ring -- in particular the 160 KB of rings of a dedicated exchange
+  // CTA, which reuse the stage region and whatever follows it -- can ever overlap it.
+  const uint32_t smem_aligned = (ptx::smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t bar_base = smem_aligned;
+  const uint32_t smem_base = smem_aligned + kSmemBarrierBytes;          // operand stages
   const int ring_bytes = p.stages * stage_bytes_cg(s.block_n, CG);
-  const uint32_t bar_base = smem_base + ring_bytes;
-  const uint32_t epi_stage = bar_base + kSmemBarrierBytes;
+  const uint32_t epi_stage = smem_base + ring_bytes;
   const uint32_t xchg_ring = epi_stage + kEpilogueStageBytes;
-  uint8_t* gen_base = smem_raw + (smem_base - ptx::smem_u32(smem_raw));
-  volatile uint32_t* s_words = reinterpret_cast<volatile uint32_t*>(gen_base + ring_bytes + 8 * BAR_COUNT);
+  uint8_t* gen_base = smem_raw + (smem_aligned - ptx::smem_u32(smem_raw));
+  volatile uint32_t* s_words = reinterpret_cast<volatile uint32_t*>(gen_base + 8 * BAR_COUNT);
   volatile uint32_t* s_tmem = s_words;       // TMEM base address
   volatile uint32_t* s_abort = s_words + 1;  // CTA-wide abort flag
   volatile uint32_t* s_epoch = s_words + 2;

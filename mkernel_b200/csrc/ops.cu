@@ -156,6 +156,9 @@ static int make_plan(int op, int rank, int world, int M, int N, int K, int b_lay
     pl.ring_slots = kRingInCtaDeep;
   pl.stages = num_stages_cg(bn, pl.cg, pl.ring_slots);
   pl.smem = smem_bytes_cg(bn, pl.cg, pl.ring_slots);
+  // a dedicated exchange CTA lays 8 warp rings over the stage region and what follows it
+  if (pl.smem < 1024 + kSmemBarrierBytes + 8 * kRingDedicated * 32 * 16)
+    return set_error(MK_ERR_INVALID, "internal: shared-memory plan too small for exchange rings");
   pl.n_comm = n_comm;
   pl.grid = n_comm + n_comp;
   *out = pl;

@@ -32,7 +32,7 @@ constexpr int kEpilogueStageBytes = 16384;  // 4 epilogue warps x 32 rows x 128 
 constexpr int kInCtaRingBytes = kRingInCta * 32 * 16;
 constexpr int kMaxStages = 8;
 constexpr int kSmemBudget = 232448;    // 227 KiB opt-in limit per CTA on sm_100
-constexpr int kSmemBarrierBytes = 512;
+constexpr int kSmemBarrierBytes = 1024;  // barriers + control words, FIRST in shared memory
 
 enum OpKind : int { OP_GEMM = 0, OP_AG = 1, OP_RS = 2, OP_AR = 3 };
 
