@@ -397,9 +397,8 @@ __device__ __forceinline__ void accumulate_bf16x8(float (&acc)[8], const uint4& 
 
 // AllGather item: copy `n_vec` 16-byte vectors from the own shard to the same offset of the
 // destination (a peer's buffer or the multicast alias) through the lane-private ring.
-// The ring is used as NS steps of VP vectors per lane; one cp.async commit group per step.
-// The number of groups in flight is kept small (<= 12): with one group per vector and a 96-slot
-// ring (95 groups outstanding) a worker never returned from its wait on this hardware.
+// The ring is used as NS steps of VP vectors per lane; one cp.async commit group per step, so
+// the number of commit groups in flight stays small (<= 12) however deep the ring is.
 template <int R>
 __device__ __forceinline__ void push_span(const char* src, char* dst, long long n_vec, bool nvls,
                                           uint32_t ring, int lane) {
