@@ -142,7 +142,9 @@ int mk_gemm_rs_launch_noalloc(const void* A, const void* B, void* C, int M, int 
  * (include/operators/gemm_ar/gemm_ar_blackwell.cuh:205-246, src/gemm_ar_blackwell.cu:57-610).
  * A: [M, K_local], B: [K_local, N] (MK_B_KN) or [N, K_local] (MK_B_NK).  C: symmetric [M, N]
  * partial product.  C_final: symmetric [M, N], complete on every rank when the launch ends.
- * barrier: symmetric MK_AR_BARRIER_WORDS, zeroed once.  epoch: strictly increasing from 1. */
+ * barrier: symmetric MK_AR_BARRIER_WORDS, zeroed once.  epoch: strictly increasing from 1 (the
+ * reference's contract), or 0 to let the library keep the epoch in `barrier` itself, which makes
+ * the launch replayable from a CUDA graph. */
 int mk_gemm_ar_launch(const void* A, const void* B, const mk_symm_view* C,
                       const mk_symm_view* barrier, const mk_symm_view* C_final, int M, int N,
                       int K, uint32_t epoch, int b_layout, void* stream);

@@ -707,10 +707,9 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
   if (threadIdx.x == 0) {
     *s_abort = 0u;
     uint32_t e = p.epoch_arg;
-    // AG / RS: the epoch lives on the device (graph replays need no host state) unless the
-    // caller supplies one (the multi-node style signatures pass a host epoch)
-    if (p.sync != nullptr && (OP == OP_AG || OP == OP_RS) && e == 0u)
-      e = ptx::ld_relaxed_sys(p.sync + SW_EPOCH) + 1u;
+    // The epoch lives on the device (graph replays need no host state) unless the caller
+    // supplies one (GEMM+AR and the multi-node style signatures pass a host epoch)
+    if (p.sync != nullptr && e == 0u) e = ptx::ld_relaxed_sys(p.sync + SW_EPOCH) + 1u;
     *s_epoch = e;
     if (!is_comm) {
       for (int i = 0; i < kMaxStages; ++i) {
@@ -807,7 +806,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
     p.sync[SW_GRID_DONE] = 0u;
     p.sync[SW_NEXT_ITEM] = 0u;
     p.sync[SW_ITEMS_DONE] = 0u;
-    if (OP == OP_RS || OP == OP_AG) p.sync[SW_EPOCH] = epoch;
+    p.sync[SW_EPOCH] = epoch;
     __threadfence();
   }
 }

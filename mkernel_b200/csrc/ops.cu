@@ -590,7 +590,6 @@ int mk_gemm_ar_launch(const void* A, const void* B, const mk_symm_view* C,
                       int K, uint32_t epoch, int b_layout, void* stream) {
   if (!A || !B) return set_error(MK_ERR_INVALID, "mk_gemm_ar_launch: null operand");
   if (M < 1 || N < 1) return set_error(MK_ERR_INVALID, "mk_gemm_ar_launch: bad shape");
-  if (epoch == 0) return set_error(MK_ERR_INVALID, "mk_gemm_ar_launch: epoch must start at 1");
   if (b_layout != MK_B_KN && b_layout != MK_B_NK)
     return set_error(MK_ERR_INVALID, "mk_gemm_ar_launch: unknown B layout %d", b_layout);
   int rc = check_view(C, "C", (size_t)M * N * 2);

@@ -20,7 +20,13 @@ gemm_rs_blackwell_sync_shape = (_lib.MK_RS_SYNC_WORDS,)
 gemm_ar_blackwell_barrier_shape = (2, 1024, 1024)
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def _stream() -> ctypes.c_void_p:
+    """The current torch CUDA stream of the current device as a raw cudaStream_t."""
+    if _raw_stream is not None:
+        return ctypes.c_void_p(_raw_stream(torch.cuda.current_device()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 
@@ -141,7 +147,8 @@ def gemm_ar_intranode_blackwell(A: torch.Tensor, B: torch.Tensor, C: DistBuffer,
         N = B.size(0)
     for d, n in ((C, "C"), (C_final, "C_final")):
         _require(d.dtype == torch.bfloat16 and tuple(d.shape) == (M, N), f"{n} must be bf16 [{M},{N}]")
-    _require(int(epoch) >= 1, "epoch starts at 1 and must increase by one per call")
+    _require(int(epoch) >= 0, "epoch starts at 1 and must increase by one per call "
+                              "(0 = keep the epoch on the device; graph-replayable)")
     with _on_device(C.local_rank_):
         _lib.check(_lib.lib().mk_gemm_ar_launch(A.data_ptr(), B.data_ptr(), C.view_ref(),
                                                 barrier.view_ref(), C_final.view_ref(), M, N, K,

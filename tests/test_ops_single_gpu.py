@@ -93,9 +93,15 @@ def test_gemm_ar_world1(layout):
         torch.cuda.synchronize()
         assert orc.rel_error(C.data_.cpu(), partials[0]) <= orc.REL_TOL     # local partial
         assert orc.rel_error(Cf.data_.cpu(), total) <= orc.REL_TOL          # reduced output
-    # M outside the reference's {2048..32768} table is an ordinary case here, and epoch 0 is an error
+    # M outside the reference's {2048..32768} table is an ordinary case here; a negative epoch is
+    # an error, and epoch 0 hands the epoch to the device (continues from the last launch)
     with pytest.raises(RuntimeError):
-        mod.gemm_ar_intranode_blackwell(A, B, C, barrier, Cf, 0, layout)
+        mod.gemm_ar_intranode_blackwell(A, B, C, barrier, Cf, -1, layout)
+    Cf.data_.zero_()
+    mod.gemm_ar_intranode_blackwell(A, B, C, barrier, Cf, 0, layout)
+    torch.cuda.synchronize()
+    assert orc.rel_error(Cf.data_.cpu(), total) <= orc.REL_TOL
+    assert int(barrier.data_.view(-1)[8]) == 3
 
 
 def test_shape_errors_raise():
