@@ -408,6 +408,97 @@ def run_ours(args):
         dst.dist.destroy_process_group()
 
 
+def run_sweep(args):
+    """BASELINE config 5: AllGather+GEMM and GEMM+ReduceScatter at total M in {2048, 8192, 32768},
+    K = 8192, global N = 28672 sharded by the world size.  Prints one JSON line {"sweep": [...]}
+    with TFLOP/s per GPU, the fused-roofline fraction and the unfused cuBLAS(+NCCL) time."""
+    import mkernel_b200
+
+    dst = Dist(args.gpus)
+    W, rank, dev = dst.world, dst.local_rank, dst.device
+    peaks, _ = load_peaks()
+    ag = mkernel_b200.load("ag_gemm_warp_specialized")
+    rs = mkernel_b200.load("gemm_rs_blackwell")
+    out = []
+    steps = max(5, min(args.steps, 20))
+    for M in (2048, 8192, 32768):
+        K, NG = 8192, 28672
+        Nl = NG // W
+        # ---- AllGather + GEMM: A_r [M/W, K], B_r [Nl, K] -> C [M, Nl]
+        Ms = M // W
+        A = ag.DistBuffer((W, Ms, K), dtype=torch.bfloat16, local_rank=rank, local_world_size=W)
+        ready = ag.DistBuffer((ag.ag_gemm_warp_specialized_ready_words,), dtype=torch.int32,
+                              local_rank=rank, local_world_size=W)
+        ready.data_.zero_()
+        A.data_.zero_()
+        A.data_[rank].copy_(randn_bf16((Ms, K), 4 + rank, dev))
+        B = randn_bf16((Nl, K), 404 + rank, dev, K ** -0.5)
+        C = torch.empty((W, Ms, Nl), device=dev, dtype=torch.bfloat16)
+        A_full = torch.empty((M, K), device=dev, dtype=torch.bfloat16)
+        C2 = torch.empty((M, Nl), device=dev, dtype=torch.bfloat16)
+        dst.barrier()
+
+        def ag_step(i, e0, e1):
+            ag.ag_gemm_warp_specialized_prepare(ready, M, Nl)
+            e0.record()
+            ag.ag_gemm_warp_specialized_launch(A, ready, B, C)
+            e1.record()
+
+        def ag_unf(i, e0, e1):
+            e0.record()
+            if W > 1:
+                dst.dist.all_gather_into_tensor(A_full, A.data_[rank])
+                torch.matmul(A_full, B.t(), out=C2)
+            else:
+                torch.matmul(A.data_[rank], B.t(), out=C2)
+            e1.record()
+
+        _, f_ms = timed_loop(dst, ag_step, steps, 3)
+        ag.op_status(ready)
+        _, u_ms = timed_loop(dst, ag_unf, steps, 3)
+        out.append(op_record("AllGather+GEMM", dict(M=M, N=Nl, K=K), W, f_ms, u_ms,
+                             2.0 * M * Nl * K, (W - 1) / W * M * K * 2, peaks))
+        A.free(); ready.free()
+        del B, C, A_full, C2
+        # ---- GEMM + ReduceScatter: A_r [M, NG/W], B_r [K, NG/W] -> out_r [M/W, K]
+        Kl, N3 = NG // W, K
+        A3 = randn_bf16((M, Kl), 4 + rank, dev)
+        B3 = randn_bf16((N3, Kl), 504 + rank, dev, NG ** -0.5)
+        C3 = rs.DistBuffer((M, N3), dtype=torch.bfloat16, local_rank=rank, local_world_size=W)
+        s3 = rs.DistBuffer(rs.gemm_rs_blackwell_sync_shape, dtype=torch.int32, local_rank=rank,
+                           local_world_size=W)
+        rs.gemm_rs_blackwell_prepare(A3, B3, C3, s3)
+        c3 = torch.empty((M, N3), device=dev, dtype=torch.bfloat16)
+        c3r = torch.empty((M // W, N3), device=dev, dtype=torch.bfloat16)
+        dst.barrier()
+
+        def rs_step(i, e0, e1):
+            e0.record()
+            rs.gemm_rs_blackwell_launch(A3, B3, C3, s3)
+            e1.record()
+
+        def rs_unf(i, e0, e1):
+            e0.record()
+            torch.mm(A3, B3.t(), out=c3)
+            if W > 1:
+                dst.dist.reduce_scatter_tensor(c3r, c3)
+            e1.record()
+
+        _, f_ms = timed_loop(dst, rs_step, steps, 3)
+        rs.op_status(s3)
+        _, u_ms = timed_loop(dst, rs_unf, steps, 3)
+        out.append(op_record("GEMM+ReduceScatter", dict(M=M, N=N3, K=Kl), W, f_ms, u_ms,
+                             2.0 * M * N3 * Kl, (W - 1) / W * M * N3 * 2, peaks))
+        C3.free(); s3.free()
+        del A3, B3, c3, c3r
+        torch.cuda.empty_cache()
+    if dst.rank == 0:
+        print(json.dumps({"sweep": out, "n_gpus": W, "peak_tflops": peaks["bf16_tflops"]}), flush=True)
+    dst.barrier()
+    if dst.dist is not None:
+        dst.dist.destroy_process_group()
+
+
 def plan_summary(_lib, W, rank):
     out = {}
     for name, op, cfg, layout in (("ag_gemm", _lib.OP_AG, CFG2, 0), ("gemm_rs", _lib.OP_RS, CFG3, 0),
@@ -513,8 +604,12 @@ def main():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--sweep", action="store_true",
+                    help="time the M x world-size sweep (BASELINE config 5) instead of the headline")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.sweep:
+        run_sweep(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

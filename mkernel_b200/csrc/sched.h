@@ -29,7 +29,6 @@ constexpr int kGatherSub = 32;         // AllGather: a 128-row block lands as 32
 constexpr int kRingDedicated = 40;     // 16-byte ring slots per lane, warps of an exchange CTA
 constexpr int kRingInCta = 32;         // same for the exchange warp inside a compute CTA (16 KB)
 constexpr int kEpilogueStageBytes = 16384;  // 4 epilogue warps x 32 rows x 128 B transpose buffers
-constexpr int kInCtaRingBytes = kRingInCta * 32 * 16;
 constexpr int kMaxStages = 8;
 constexpr int kSmemBudget = 232448;    // 227 KiB opt-in limit per CTA on sm_100
 constexpr int kSmemBarrierBytes = 1024;  // barriers + control words, FIRST in shared memory
@@ -217,14 +216,6 @@ MKB_HD int stage_bytes(int block_n) { return kBlockM * kBlockK * 2 + block_n * k
 // Same for a CTA pair (cg = 2): each CTA holds its A tile and half of the B tile.
 MKB_HD int stage_bytes_cg(int block_n, int cg) {
   return kBlockM * kBlockK * 2 + (block_n / cg) * kBlockK * 2;
-}
-constexpr int kSmemFixedBytes = 1024 + kSmemBarrierBytes + kEpilogueStageBytes + kInCtaRingBytes;
-MKB_HD int num_stages(int block_n) {
-  int n = (kSmemBudget - kSmemFixedBytes) / stage_bytes(block_n);
-  return n > kMaxStages ? kMaxStages : n;
-}
-MKB_HD int smem_bytes(int block_n) {
-  return kSmemFixedBytes + num_stages(block_n) * stage_bytes(block_n);
 }
 // `ring_slots` = 16-byte ring slots per lane of the in-CTA exchange warp (32 -> 16 KB, 96 -> 48 KB).
 MKB_HD int smem_fixed_bytes(int ring_slots) {
