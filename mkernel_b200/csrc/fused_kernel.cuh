@@ -436,6 +436,57 @@ __device__ __forceinline__ void push_span(const char* src, char* dst, long long 
   ptx::cp_async_wait<0>();
 }
 
+// Same copy, but every step (VP x 32 vectors = one contiguous range in both the ring and the
+// destination) leaves as ONE bulk store issued by lane 0: fewer, larger write requests on NVLink.
+template <int R>
+__device__ __forceinline__ void push_span_bulk(const char* src, char* dst, long long n_vec,
+                                               uint32_t ring, int lane) {
+  constexpr int VP = R >= 64 ? 8 : 4;
+  constexpr int NS = R / VP;
+  static_assert(NS >= 3 && NS <= 12 && NS * VP == R, "ring geometry");
+  const long long n_mine = n_vec > lane ? (n_vec - 1 - lane) / 32 + 1 : 0;
+  const long long n_steps = (n_vec + VP * 32 - 1) / (VP * 32);          // same for every lane
+  auto off = [&](long long e) { return (e * 32 + lane) * 16; };
+  auto slot = [&](long long e) { return ring + (static_cast<uint32_t>(e % R) * 32u + lane) * 16u; };
+  auto issue = [&](long long st) {
+    if (st < n_steps) {
+#pragma unroll
+      for (int j = 0; j < VP; ++j) {
+        const long long e = st * VP + j;
+        if (e < n_mine) ptx::cp_async_16(slot(e), src + off(e));
+      }
+    }
+    ptx::cp_async_commit();
+  };
+  // The slots of step st are refilled by step st + NS - 2, issued after the bulk store of step
+  // st - 1 ... so one ring step is always either being stored or free: NS - 2 steps in flight.
+  for (long long st = 0; st < NS - 2; ++st) issue(st);
+  for (long long st = 0; st < n_steps; ++st) {
+    // the step about to be refilled was stored two iterations ago: its store must have read it
+    if (lane == 0) ptx::bulk_wait_read<1>();
+    __syncwarp();
+    issue(st + NS - 2);
+    ptx::cp_async_wait<NS - 2>();
+    ptx::fence_proxy_async();       // cp.async wrote the ring; the bulk store reads it
+    __syncwarp();
+    if (lane == 0) {
+      const long long first = st * VP * 32;
+      long long vecs = n_vec - first;
+      if (vecs > VP * 32) vecs = VP * 32;
+      ptx::bulk_s2g(dst + first * 16,
+                    ring + static_cast<uint32_t>((st * VP) % R) * 512u,
+                    static_cast<uint32_t>(vecs * 16));
+      ptx::bulk_commit();
+    }
+  }
+  ptx::cp_async_wait<0>();
+  if (lane == 0) {
+    ptx::bulk_wait_all<0>();   // every byte has been written before the flag goes out
+    ptx::fence_proxy_async();
+  }
+  __syncwarp();
+}
+
 struct ReduceSpan {
   const char* src[kMaxWorld];  // W copies of the same byte range
   char* dst[kMaxWorld];        // RS: dst[0] only; AR: every rank's output
@@ -569,7 +620,10 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
         if (!__all_sync(0xffffffffu, ok)) return;
         for (int r = first; r <= last; ++r) entered_mask |= 1u << r;
       }
-      if (!(p.debug_flags & 1)) push_span<R>(local + base, dst + base, n_vec, nvls_ag, ring, lane);
+      if (!(p.debug_flags & 1)) {
+        if (p.push_bulk && !nvls_ag) push_span_bulk<R>(local + base, dst + base, n_vec, ring, lane);
+        else push_span<R>(local + base, dst + base, n_vec, nvls_ag, ring, lane);
+      }
       __syncwarp();
       if (lane == 0) {
         ptx::fence_acq_rel_sys();
@@ -589,7 +643,15 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
       uint32_t* summary = p.sync + SW_FLAGS + summary_flag_index(s, rb);
       bool ready = ptx::ld_acquire_gpu(summary) == epoch;
       ready = __shfl_sync(0xffffffffu, ready, 0);
-      if (!ready) {
+      if (!ready && c != 0) {
+        // Only the worker holding the first chunk of a piece polls the W x Q tile flags (items
+        // are handed out in order, so somebody always holds it); everybody else waits for the
+        // one summary word instead of hammering the lines the peers are writing to.
+        const bool ok = bounded_wait<true>(wc, [&] { return ptx::ld_acquire_gpu(summary) == epoch; },
+                                           ST_TIMEOUT_TILE, rb, 1);
+        if (!__all_sync(0xffffffffu, ok)) return;
+        ptx::fence_acq_rel_sys();
+      } else if (!ready) {
         bool ok = true;
         if ((s.Q & 3) == 0) {
           // The Q flags of one source rank are contiguous: poll them four at a time, all of a

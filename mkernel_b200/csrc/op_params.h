@@ -14,6 +14,7 @@ struct OpParams {
   int n_comm;            // CTAs [0, n_comm) run only the exchange role, the rest run the GEMM
   int item_vecs;         // RS/AR: 16-byte vectors per exchange work item
   int n_items;           // exchange work items of this rank for this launch
+  int push_bulk;         // AllGather push: leave each ring step as one TMA bulk store
   int ring_slots;        // ring depth (16-byte slots per lane) of the in-CTA exchange warp
   int use_nvls;          // exchange through NVSwitch multicast addresses when available
   int debug_flags;       // timing diagnostics only (results undefined): 1 = exchange workers skip

@@ -30,6 +30,7 @@ struct Options {
   long long group_rows = 0;
   long long use_nvls = 0;
   long long debug_flags = 0;
+  long long push_bulk = 0;   // AllGather push through TMA bulk stores instead of LSU stores
   long long ar_one_shot = 0;  // GEMM+AR: 1 = every rank reduces all rows itself (no broadcast)
   long long cta_pair = 1;   // 1: run compute CTAs as pairs (two-SM MMA) when the shape allows
 };
@@ -45,6 +46,7 @@ static long long* option_slot(const char* name) {
   if (!strcmp(name, "use_nvls")) return &g_opt.use_nvls;
   if (!strcmp(name, "cta_pair")) return &g_opt.cta_pair;
   if (!strcmp(name, "debug_flags")) return &g_opt.debug_flags;
+  if (!strcmp(name, "push_bulk")) return &g_opt.push_bulk;
   if (!strcmp(name, "ar_one_shot")) return &g_opt.ar_one_shot;
   return nullptr;
 }
@@ -330,6 +332,7 @@ static int run_op(const OpArgs& a, cudaStream_t stream) {
     std::lock_guard<std::mutex> g(g_opt_mu);
     want_nvls = g_opt.use_nvls != 0;
     p.debug_flags = (int)g_opt.debug_flags;
+    p.push_bulk = (int)g_opt.push_bulk;
   }
   if (a.world > 1 && a.op != OP_GEMM) {
     const int workers = (pl.grid - pl.n_comm) + 8 * pl.n_comm;

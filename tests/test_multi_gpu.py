@@ -84,3 +84,17 @@ def test_baseline_shapes_sampled_rows():
         dict(op="ar", M=128, N=8192, K=1024, seed=3, iters=3, max_rows=128),
     ]
     check(launch(world, cases, timeout=900))
+
+
+@pytest.mark.skipif(n_gpus() < 2, reason="needs at least 2 GPUs")
+def test_allgather_variants():
+    """The AllGather push through TMA bulk stores, and the one-shot AllReduce, give the same
+    results as the defaults."""
+    world = min(n_gpus(), 8)
+    world = 1 << (world.bit_length() - 1)
+    cases = [
+        dict(op="ag", M=world * 256, N=264, K=1024, seed=1, iters=2, max_rows=4096),
+        dict(op="ag", M=world * 72, N=512, K=200, seed=1, iters=2, max_rows=4096),
+        dict(op="ar", M=128, N=1024, K=256, seed=3, iters=2, max_rows=4096),
+    ]
+    check(launch(world, cases, options={"push_bulk": 1, "ar_one_shot": 1}))
