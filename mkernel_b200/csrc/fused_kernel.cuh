@@ -818,14 +818,6 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
     if (OP != OP_GEMM)
       exchange_worker<OP, kRingDedicated>(p, smem_base + warp * (kRingDedicated * 32 * 16), wc,
                                           epoch, s_item + warp);
-  } else if (OP == OP_AG && (warp == 2 || warp == 3)) {
-    // AllGather has no tile publisher, so warps 2 and 3 both push, each with half of the ring:
-    // the push rate is set by how many warps issue remote stores, not by bytes in flight.
-    const uint32_t half = xchg_ring + (warp == 3 ? static_cast<uint32_t>(p.ring_slots / 2) * 512u : 0u);
-    if (p.ring_slots == kRingInCtaDeep)
-      exchange_worker<OP, kRingInCtaDeep / 2>(p, half, wc, epoch, s_item + warp);
-    else
-      exchange_worker<OP, kRingInCta / 2>(p, half, wc, epoch, s_item + warp);
   } else if (warp == 3) {
     if (OP != OP_GEMM) {
       if (p.ring_slots == kRingInCtaDeep)
