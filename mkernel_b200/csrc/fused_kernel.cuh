@@ -13,7 +13,7 @@
 // GEMM cannot fill the machine anyway, e.g. the decode-shaped AllReduce).
 //
 // Exchange work items (handed out in order by an atomic counter, so early items meet early data):
-//   AllGather      push one 16-row group of the own A shard into a peer's gathered buffer with
+//   AllGather      push one 4-row group of the own A shard into a peer's gathered buffer with
 //                  posted remote stores (or into all peers with one NVSwitch multicast store),
 //                  then fence and raise the group's flag on the receiver.
 //   ReduceScatter  GEMM tiles were stored straight into the owner's buffer (slab = producing
@@ -593,10 +593,12 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
     if (item >= p.n_items) break;
 
     if (OP == OP_AG) {
-      const int groups = s.part_blocks * kGatherSub;
-      const int d = nvls_ag ? 0 : 1 + item / groups;       // ring distance of the receiver
-      const int jg = item % groups;
-      const int j = jg / kGatherSub, g = jg % kGatherSub;
+      // Item order: row-block j of the own shard goes to every receiver (nearest ring distance
+      // first) before row-block j+1 goes to anybody -- the order in which receivers consume.
+      const int per_block = (nvls_ag ? 1 : W - 1) * kGatherSub;
+      const int j = item / per_block;
+      const int d = nvls_ag ? 0 : 1 + (item % per_block) / kGatherSub;   // receiver's ring distance
+      const int g = item % kGatherSub;
       const int rowblock = s.rank * s.part_blocks + j;
       const int rows_in_block = rowblock_rows(s, rowblock);
       const int r0 = g * (kBlockM / kGatherSub);

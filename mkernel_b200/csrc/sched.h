@@ -7,7 +7,8 @@
 // same functions can be unit-tested on the host through the C ABI (mk_sched_* functions).
 //
 // Reference behaviour restated here (not its code): AllGather+GEMM visits the local shard first
-// and then shards at ring distance 1..W-1 (src/ag_gemm_warp_specialized.cu:243); the
+// and then the shards at ring distance 1..W-1 (src/ag_gemm_warp_specialized.cu:243; here the
+// remote shards are interleaved by row-block to match the order in which pushes arrive); the
 // reduce-scatter family interleaves the owners' slices so every owner's tiles become complete
 // progressively (include/operators/gemm_rs/gemm_rs.cuh:279-353).
 #pragma once
@@ -93,12 +94,18 @@ MKB_HD Sched make_sched(int op, int rank, int world, int M, int N, int block_n, 
 }
 
 // i-th row-block in visiting order -> row-block id.
-//   AG: id = shard * part_blocks + j, shards visited local first then ring distance 1..W-1.
+//   AG: id = shard * part_blocks + j; the local shard first, then the remote shards
+//   row-block-major (block j of ring distance 1..W-1, then block j+1, ...).
 //   RS/AR (interleaved): j-th block of owner (rank+1+d) % W, d fastest, so the own slice is last
 //   inside each round and every owner receives complete row-blocks round by round.
 MKB_HD int order_to_rowblock(const Sched& s, int i) {
   if (s.op == OP_AG) {
-    const int d = i / s.part_blocks, j = i % s.part_blocks;
+    // local shard first; then block j of every remote shard (ring distance 1..W-1) before block
+    // j+1 of any: the senders push block j of their shard to everybody before block j+1, so
+    // rows are consumed in the order in which they arrive
+    if (i < s.part_blocks || s.world == 1) return s.rank * s.part_blocks + i;
+    const int idx = i - s.part_blocks;
+    const int j = idx / (s.world - 1), d = 1 + idx % (s.world - 1);
     return ((s.rank + d) % s.world) * s.part_blocks + j;
   }
   if (s.interleave) {

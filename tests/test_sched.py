@@ -51,16 +51,22 @@ def test_every_output_element_is_covered_once(op, world, M, N, K, layout):
         assert area == M * N
 
 
-def test_allgather_visits_local_shard_first_then_ring():
+def test_allgather_visits_local_shard_first_then_remote_rows_in_arrival_order():
     world, M, N = 8, 8192, 3584
+    rb_per_shard = M // world // 128
     for rank in (0, 3, 7):
         tiles = _lib.sched_tiles(OP_AG, rank, world, M, N, 256, 8)
-        shards = [row0 // (M // world) for row0, _, _, _ in tiles]
-        order = []
-        for s in shards:
-            if not order or order[-1] != s:
-                order.append(s)
-        assert order == [(rank + d) % world for d in range(world)]
+        seen = []                       # row-blocks in first-visit order: (shard, block)
+        for row0, _, _, _ in tiles:
+            key = (row0 // (M // world), (row0 % (M // world)) // 128)
+            if key not in seen:
+                seen.append(key)
+        assert seen[:rb_per_shard] == [(rank, j) for j in range(rb_per_shard)]
+        rest = seen[rb_per_shard:]
+        expect = [((rank + d) % world, j) for j in range(rb_per_shard) for d in range(1, world)]
+        # groups of 8 row-blocks are rastered together, so compare as sets per raster group
+        for g in range(0, len(rest), 8):
+            assert sorted(rest[g:g + 8]) == sorted(expect[g:g + 8])
 
 
 def test_reduce_scatter_interleaves_owners_own_slice_last():
