@@ -110,6 +110,13 @@ __device__ __forceinline__ bool wait_mbar(const WaitCtx& c, uint32_t bar, uint32
                              ST_TIMEOUT_PIPE, d0, parity);
 }
 
+// Timing diagnostics (debug_flags & 4): low 32 bits of %globaltimer at a few protocol events,
+// written to the otherwise unused sync words [24, 32).
+__device__ __forceinline__ void stamp(const OpParams& p, int slot) {
+  if ((p.debug_flags & 4) && p.sync != nullptr)
+    p.sync[24 + slot] = static_cast<uint32_t>(global_timer_ns());
+}
+
 struct TileInfo {
   int rowblock, q, row0, rows, n0;
 };
@@ -287,6 +294,7 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
         rowblock_owners(s, ti.rowblock, &lo, &hi);
         const long long idx = SW_FLAGS + tile_flag_index(s, s.rank, ti.rowblock, ti.q);
         for (int o = lo; o <= hi; ++o) ptx::st_relaxed_sys(p.peer_sync[o] + idx, epoch);
+        if (t == 0) stamp(p, 1);
         if (CG == 1) ptx::mbar_arrive(bar(BAR_TEMPTY + acc));
         else ptx::mbar_arrive_cluster(lead(BAR_TEMPTY + acc));
         acc ^= 1;
@@ -652,7 +660,6 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
         const bool ok = bounded_wait<true>(wc, [&] { return ptx::ld_acquire_gpu(summary) == epoch; },
                                            ST_TIMEOUT_TILE, rb, 1);
         if (!__all_sync(0xffffffffu, ok)) return;
-        ptx::fence_acq_rel_sys();
       } else if (!ready) {
         bool ok = true;
         if ((s.Q & 3) == 0) {
@@ -679,6 +686,7 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
           }
         }
         if (!__all_sync(0xffffffffu, ok)) return;
+        if (lane == 0) stamp(p, 2);
         if (lane == 0) ptx::st_release_gpu(summary, epoch);
       }
       // 2. sum this chunk of the piece
@@ -725,6 +733,7 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
     if (OP == OP_AR && lane == 0) {
       const uint32_t done = atomicAdd(p.sync + SW_ITEMS_DONE, 1u);
       if (done == static_cast<uint32_t>(p.n_items - 1)) {
+        stamp(p, 3);
         ptx::fence_acq_rel_sys();
         for (int r = 0; r < W; ++r) ptx::st_relaxed_sys(p.peer_sync[r] + SW_EXIT + s.rank, epoch);
       }
@@ -791,6 +800,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
       ptx::tma_prefetch_desc(&tma_b);
     }
     ptx::fence_mbar_init();
+    if (blockIdx.x == 0) stamp(p, 0);
     if (blockIdx.x == 0 && p.sync != nullptr && s.world > 1) {
       // AG / RS: tell every rank that this rank has entered launch e, i.e. that its previous
       // launch has ended and its buffers may be written again (replaces an all-rank barrier).
@@ -859,6 +869,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
     // its exchange work (this rank's output is complete, nobody still reads its partials).
     // AG / RS need no such wait: their results are produced by this rank's own CTAs, and the
     // next launch's writers wait for the entry flag instead.
+    stamp(p, 4);
     if (OP == OP_AR && s.world > 1 && *s_abort == 0u) {
       for (int r = 0; r < s.world; ++r) {
         const uint32_t* f = p.sync + SW_EXIT + r;
@@ -867,6 +878,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
           break;
       }
     }
+    stamp(p, 5);
     p.sync[SW_GRID_DONE] = 0u;
     p.sync[SW_NEXT_ITEM] = 0u;
     p.sync[SW_ITEMS_DONE] = 0u;

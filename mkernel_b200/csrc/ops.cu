@@ -63,16 +63,11 @@ struct Plan {
 };
 
 static int default_n_comm(int op, int world, int M, int N, int K, int num_sms) {
-  (void)K;
-  if (world <= 1 || op == OP_GEMM) return 0;
-  // Every compute CTA carries one exchange warp, which is enough when the GEMM fills the
-  // machine.  Small, latency-bound problems cannot give every SM a tile even at the narrowest
-  // tile width: the SMs left over (up to 32) become dedicated exchange CTAs with 8 workers each.
-  const long long tiles64 = (long long)ceil_div(M, kBlockM) * ceil_div(N, 64);
-  if (tiles64 + 2 <= num_sms) {
-    int spare = num_sms - (int)tiles64;
-    return spare > 32 ? 32 : spare;
-  }
+  // Every compute CTA carries one exchange warp.  Dedicated exchange CTAs (8 workers each) can be
+  // requested with the n_comm option; measured on B200 they did not help, not even for the
+  // decode-shaped AllReduce (more workers contend on the item queue and on system-scope fences:
+  // 21 us against 15 us for the reduce phase at W = 4), so the default is none.
+  (void)op; (void)world; (void)M; (void)N; (void)K; (void)num_sms;
   return 0;
 }
 
