@@ -160,7 +160,11 @@ int mk_op_status_clear(const mk_symm_view* sync, void* stream);
  *      "use_nvls" (0/1: exchange through NVSwitch multicast when the buffers have an alias),
  *      "cta_pair" (0/1, default 1: two-SM MMA over CTA pairs when the shape allows),
  *      "ar_one_shot" (GEMM+AR: 0 = two-shot, owners reduce and broadcast; 1 = one-shot, every
- *      rank reduces all rows for itself), "debug_flags" (timing diagnostics; results undefined). */
+ *      rank reduces all rows for itself), "ag_fanout" (AllGather push: 0 = one work item per
+ *      receiver, 1 = an item loads its rows once and stores them to every peer), "push_bulk"
+ *      (AllGather push through bulk shared-to-global stores), "debug_flags" (timing diagnostics;
+ *      results undefined).  The environment variable MKERNEL_B200_OPTIONS="name=value,..." sets
+ *      start-up defaults when the library is loaded. */
 int mk_set_option(const char* name, long long value);
 long long mk_get_option(const char* name);
 

@@ -444,6 +444,48 @@ __device__ __forceinline__ void push_span(const char* src, char* dst, long long 
   ptx::cp_async_wait<0>();
 }
 
+// Same copy with fan-out: every vector is loaded once and stored to all `n_dst` destinations
+// (the same offset of every peer's buffer), nearest ring distance first.
+template <int R>
+__device__ __forceinline__ void push_span_fanout(const char* src, char* const (&dst)[kMaxWorld],
+                                                 int n_dst, long long n_vec, uint32_t ring,
+                                                 int lane) {
+  constexpr int VP = R >= 64 ? 8 : 4;
+  constexpr int NS = R / VP;
+  static_assert(NS >= 2 && NS <= 12 && NS * VP == R, "ring geometry");
+  const long long n_mine = n_vec > lane ? (n_vec - 1 - lane) / 32 + 1 : 0;
+  const long long n_steps = (n_mine + VP - 1) / VP;
+  auto off = [&](long long e) { return (e * 32 + lane) * 16; };
+  auto slot = [&](long long e) { return ring + (static_cast<uint32_t>(e % R) * 32u + lane) * 16u; };
+  auto issue = [&](long long st) {
+    if (st < n_steps) {
+#pragma unroll
+      for (int j = 0; j < VP; ++j) {
+        const long long e = st * VP + j;
+        if (e < n_mine) ptx::cp_async_16(slot(e), src + off(e));
+      }
+    }
+    ptx::cp_async_commit();
+  };
+  for (long long st = 0; st < NS - 1; ++st) issue(st);
+  for (long long st = 0; st < n_steps; ++st) {
+    issue(st + NS - 1);
+    ptx::cp_async_wait<NS - 1>();
+#pragma unroll
+    for (int j = 0; j < VP; ++j) {
+      const long long e = st * VP + j;
+      if (e < n_mine) {
+        const uint4 v = ptx::ld_shared_v4(slot(e));
+        const long long o = off(e);
+#pragma unroll
+        for (int d = 0; d < kMaxWorld - 1; ++d)
+          if (d < n_dst) ptx::st_global_v4(dst[d] + o, v);
+      }
+    }
+  }
+  ptx::cp_async_wait<0>();
+}
+
 // Same copy, but every step (VP x 32 vectors = one contiguous range in both the ring and the
 // destination) leaves as ONE bulk store issued by lane 0: fewer, larger write requests on NVLink.
 template <int R>
@@ -587,6 +629,8 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
   if (W <= 1 || p.n_items <= 0) return;
   wc.where = (blockIdx.x << 8) | 0x10u | (threadIdx.x >> 5);
   const bool nvls_ag = OP == OP_AG && p.use_nvls && p.mc_data != nullptr;
+  // one item serves every receiver: through the multicast alias, or by storing to each peer
+  const bool bcast_ag = nvls_ag || (OP == OP_AG && p.ag_fanout != 0);
   const bool nvls_ar = OP == OP_AR && p.use_nvls && !s.one_shot && p.mc_data != nullptr &&
                        p.mc_out != nullptr;
   const long long row_bytes = (OP == OP_AG ? static_cast<long long>(p.K) : static_cast<long long>(s.N)) * 2;
@@ -603,9 +647,9 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
     if (OP == OP_AG) {
       // Item order: row-block j of the own shard goes to every receiver (nearest ring distance
       // first) before row-block j+1 goes to anybody -- the order in which receivers consume.
-      const int per_block = (nvls_ag ? 1 : W - 1) * kGatherSub;
+      const int per_block = (bcast_ag ? 1 : W - 1) * kGatherSub;
       const int j = item / per_block;
-      const int d = nvls_ag ? 0 : 1 + (item % per_block) / kGatherSub;   // receiver's ring distance
+      const int d = bcast_ag ? 0 : 1 + (item % per_block) / kGatherSub;   // receiver's ring distance
       const int g = item % kGatherSub;
       const int rowblock = s.rank * s.part_blocks + j;
       const int rows_in_block = rowblock_rows(s, rowblock);
@@ -619,7 +663,7 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
       // The receiver's gathered buffer may be overwritten only once the receiver has entered
       // this launch (its previous launch, which read the buffer, has ended).
       {
-        const int first = nvls_ag ? 0 : dst_rank, last = nvls_ag ? W - 1 : dst_rank;
+        const int first = bcast_ag ? 0 : dst_rank, last = bcast_ag ? W - 1 : dst_rank;
         bool ok = true;
         for (int r = first + lane; r <= last && ok; r += 32) {
           if (entered_mask & (1u << r)) continue;
@@ -631,16 +675,27 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
         for (int r = first; r <= last; ++r) entered_mask |= 1u << r;
       }
       if (!(p.debug_flags & 1)) {
-        if (p.push_bulk && !nvls_ag) push_span_bulk<R>(local + base, dst + base, n_vec, ring, lane);
-        else push_span<R>(local + base, dst + base, n_vec, nvls_ag, ring, lane);
+        if (bcast_ag && !nvls_ag) {
+          char* fan[kMaxWorld];
+#pragma unroll
+          for (int i = 0; i < kMaxWorld - 1; ++i)
+            fan[i] = i < W - 1 ? static_cast<char*>(p.peer_data[(s.rank - 1 - i + W) % W]) + base
+                               : nullptr;
+          fan[kMaxWorld - 1] = nullptr;
+          push_span_fanout<R>(local + base, fan, W - 1, n_vec, ring, lane);
+        } else if (p.push_bulk && !nvls_ag) {
+          push_span_bulk<R>(local + base, dst + base, n_vec, ring, lane);
+        } else {
+          push_span<R>(local + base, dst + base, n_vec, nvls_ag, ring, lane);
+        }
       }
       __syncwarp();
       if (lane == 0) {
         ptx::fence_acq_rel_sys();
         const long long idx = SW_FLAGS + gather_flag_index(rowblock, g);
-        if (nvls_ag) {
-          for (int r = 0; r < W; ++r)
-            if (r != s.rank) ptx::st_relaxed_sys(p.peer_sync[r] + idx, epoch);
+        if (bcast_ag) {
+          for (int i = 1; i < W; ++i)
+            ptx::st_relaxed_sys(p.peer_sync[(s.rank - i + W) % W] + idx, epoch);
         } else {
           ptx::st_relaxed_sys(p.peer_sync[dst_rank] + idx, epoch);
         }

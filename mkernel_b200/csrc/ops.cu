@@ -11,8 +11,10 @@
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <string>
 
 #include "../../include/mkernel_b200.h"
 #include "fused_kernel.cuh"
@@ -30,6 +32,7 @@ struct Options {
   long long group_rows = 0;
   long long use_nvls = 0;
   long long debug_flags = 0;
+  long long ag_fanout = 0;   // AllGather push: load each row group once, store it to every peer
   long long push_bulk = 0;   // AllGather push through TMA bulk stores instead of LSU stores
   long long ar_one_shot = 0;  // GEMM+AR: 1 = every rank reduces all rows itself (no broadcast)
   long long cta_pair = 1;   // 1: run compute CTAs as pairs (two-SM MMA) when the shape allows
@@ -47,9 +50,39 @@ static long long* option_slot(const char* name) {
   if (!strcmp(name, "cta_pair")) return &g_opt.cta_pair;
   if (!strcmp(name, "debug_flags")) return &g_opt.debug_flags;
   if (!strcmp(name, "push_bulk")) return &g_opt.push_bulk;
+  if (!strcmp(name, "ag_fanout")) return &g_opt.ag_fanout;
   if (!strcmp(name, "ar_one_shot")) return &g_opt.ar_one_shot;
   return nullptr;
 }
+
+// Start-up defaults from the environment, for callers that cannot reach mk_set_option (a launcher
+// script around an unmodified host program): MKERNEL_B200_OPTIONS="use_nvls=1,block_n=256".
+// Unknown names and malformed entries are reported on stderr and skipped.
+struct EnvOptions {
+  EnvOptions() {
+    const char* env = getenv("MKERNEL_B200_OPTIONS");
+    if (!env || !*env) return;
+    std::string all(env);
+    size_t pos = 0;
+    while (pos <= all.size()) {
+      size_t end = all.find(',', pos);
+      if (end == std::string::npos) end = all.size();
+      const std::string item = all.substr(pos, end - pos);
+      pos = end + 1;
+      if (item.empty()) continue;
+      const size_t eq = item.find('=');
+      long long* slot = eq == std::string::npos ? nullptr : option_slot(item.substr(0, eq).c_str());
+      char* tail = nullptr;
+      const long long v = eq == std::string::npos ? 0 : strtoll(item.c_str() + eq + 1, &tail, 10);
+      if (!slot || !tail || *tail != 0 || tail == item.c_str() + eq + 1 || v < -1) {
+        fprintf(stderr, "mkernel_b200: ignoring MKERNEL_B200_OPTIONS entry '%s'\n", item.c_str());
+        continue;
+      }
+      *slot = v;
+    }
+  }
+};
+static EnvOptions g_env_options;
 
 // ------------------------------------------------------------------------------------------
 // planning (pure host arithmetic; also exported for tests)
@@ -328,12 +361,14 @@ static int run_op(const OpArgs& a, cudaStream_t stream) {
     want_nvls = g_opt.use_nvls != 0;
     p.debug_flags = (int)g_opt.debug_flags;
     p.push_bulk = (int)g_opt.push_bulk;
+    p.ag_fanout = (int)g_opt.ag_fanout;
   }
   if (a.world > 1 && a.op != OP_GEMM) {
     const int workers = (pl.grid - pl.n_comm) + 8 * pl.n_comm;
     if (a.op == OP_AG) {
       p.item_vecs = 0;
-      p.n_items = gather_num_items(pl.sched, want_nvls && a.data && a.data->mc != nullptr);
+      p.n_items = gather_num_items(pl.sched, p.ag_fanout != 0 ||
+                                                 (want_nvls && a.data && a.data->mc != nullptr));
     } else {
       p.item_vecs = choose_item_vecs(pl.sched, workers);
       p.n_items = reduce_num_items(pl.sched, a.rank, p.item_vecs);

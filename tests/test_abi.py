@@ -83,3 +83,20 @@ def test_loader_names():
         assert mod.get_fifo_handles() == (0, 0, 0, 0, 0)
     with pytest.raises(RuntimeError):
         mkernel_b200.load("ring_attention")
+
+
+def test_options_from_environment():
+    """MKERNEL_B200_OPTIONS sets start-up defaults; bad entries are reported and skipped."""
+    import os
+    import subprocess
+    import sys
+    env = dict(os.environ, MKERNEL_B200_OPTIONS="use_nvls=1,block_n=224,bogus=3,ag_fanout=x")
+    code = ("from mkernel_b200 import _lib; "
+            "print(_lib.get_option('use_nvls'), _lib.get_option('block_n'), "
+            "_lib.get_option('ag_fanout'))")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = subprocess.run([sys.executable, "-c", code], env=env, cwd=root, capture_output=True,
+                         text=True, timeout=120)
+    assert out.returncode == 0, out.stderr
+    assert out.stdout.split() == ["1", "224", "0"]
+    assert "bogus=3" in out.stderr and "ag_fanout=x" in out.stderr

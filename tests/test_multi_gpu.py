@@ -98,3 +98,17 @@ def test_allgather_variants():
         dict(op="ar", M=128, N=1024, K=256, seed=3, iters=2, max_rows=4096),
     ]
     check(launch(world, cases, options={"push_bulk": 1, "ar_one_shot": 1}))
+
+
+@pytest.mark.skipif(n_gpus() < 2, reason="needs at least 2 GPUs")
+def test_allgather_fanout():
+    """The AllGather push that loads a row group once and stores it to every peer gives the same
+    (bit-exact gathered operand, same product) results as the per-receiver push."""
+    world = min(n_gpus(), 8)
+    world = 1 << (world.bit_length() - 1)
+    cases = [
+        dict(op="ag", M=world * 256, N=264, K=1024, seed=1, iters=2, max_rows=4096),
+        dict(op="ag", M=world * 72, N=512, K=200, seed=1, iters=2, max_rows=4096),
+        dict(op="ag", M=world * 1024, N=512, K=2048, seed=4, iters=2, max_rows=64),
+    ]
+    check(launch(world, cases, options={"ag_fanout": 1}))
