@@ -162,7 +162,9 @@ int mk_op_status_clear(const mk_symm_view* sync, void* stream);
  *      "ar_one_shot" (GEMM+AR: 0 = two-shot, owners reduce and broadcast; 1 = one-shot, every
  *      rank reduces all rows for itself), "ag_fanout" (AllGather push: 0 = one work item per
  *      receiver, 1 = an item loads its rows once and stores them to every peer), "push_bulk"
- *      (AllGather push through bulk shared-to-global stores), "debug_flags" (timing diagnostics;
+ *      (AllGather push through bulk shared-to-global stores), "ag_lead" (AllGather push pacing:
+ *      rows are pushed at most this many quarter raster groups before the GEMM reaches the group
+ *      that consumes them; 0 = push as fast as possible), "debug_flags" (timing diagnostics;
  *      results undefined).  The environment variable MKERNEL_B200_OPTIONS="name=value,..." sets
  *      start-up defaults when the library is loaded. */
 int mk_set_option(const char* name, long long value);

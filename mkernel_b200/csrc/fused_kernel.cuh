@@ -159,7 +159,8 @@ template <int OP, int CG>
 __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CUtensorMap* tma_b,
                                               const OpParams& p, uint32_t smem_base,
                                               uint32_t bar_base, uint32_t epi_stage,
-                                              uint32_t tmem_base, WaitCtx& wc, uint32_t epoch) {
+                                              uint32_t tmem_base, WaitCtx& wc, uint32_t epoch,
+                                              volatile uint32_t* s_progress) {
   const Sched& s = p.sched;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_comp = gridDim.x - p.n_comm;
@@ -167,7 +168,7 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
   // First tile of this CTA; the stride is n_comp for both modes (pairs step by n_comp / 2).
   const int cta = CG == 2 ? (((static_cast<int>(blockIdx.x) - p.n_comm) & ~1) + crank)
                           : static_cast<int>(blockIdx.x) - p.n_comm;
-  const int total = s.P * s.Q;
+  const int total = (p.debug_flags & 32) ? 0 : s.P * s.Q;   // diagnostics: exchange only
   const int bn = s.block_n;
   const int b_rows = bn / CG;                         // B rows (columns of C) this CTA loads
   const int stage_sz = kBlockM * kBlockK * 2 + b_rows * kBlockK * 2;
@@ -184,6 +185,7 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
     bool ok = true;
     for (int t = cta; t < total && ok; t += n_comp) {
       const TileInfo ti = tile_info(s, t);
+      if (OP == OP_AG && lane == 0) *s_progress = static_cast<uint32_t>(t);
       if (OP == OP_AG && s.world > 1 && rowblock_shard(s, ti.rowblock) != s.rank) {
         // Rows of a remote shard: wait until the sender has landed all 4-row groups here.
         static_assert(kGatherSub == 32, "one group flag per producer lane");
@@ -227,6 +229,7 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
       }
       ok = __all_sync(0xffffffffu, ok);
     }
+    if (OP == OP_AG && lane == 0) *s_progress = 0x7fffffffu;   // nothing left to pace against
   } else if (warp == 1) {
     // ---------------- MMA issuer (one thread) ----------------
     wc.where = (blockIdx.x << 8) | 1u;
@@ -403,131 +406,140 @@ __device__ __forceinline__ void accumulate_bf16x8(float (&acc)[8], const uint4& 
   }
 }
 
-// AllGather item: copy `n_vec` 16-byte vectors from the own shard to the same offset of the
-// destination (a peer's buffer or the multicast alias) through the lane-private ring.
-// The ring is used as NS steps of VP vectors per lane; one cp.async commit group per step, so
-// the number of commit groups in flight stays small (<= 12) however deep the ring is.
+// The span loops below run on ONE warp next to the GEMM, so their own instruction count decides
+// how fast bytes move: all index arithmetic is 32-bit, addresses advance by constants, and a step
+// whose vectors are all in range takes a branch-free path.
+//
+// Ring geometry shared by the push loops: a ring of R slots per lane (slot = 32 lanes x 16 bytes,
+// 512 bytes) is used as NS steps of VP slots.  Vector e of a lane (the lane's e-th 16 bytes, i.e.
+// vector e * 32 + lane of the span) lives in slot e % R = (step % NS) * VP + j.  One cp.async
+// commit group per step keeps the number of groups in flight small (<= 12) however deep the ring.
 template <int R>
-__device__ __forceinline__ void push_span(const char* src, char* dst, long long n_vec, bool nvls,
-                                          uint32_t ring, int lane) {
-  constexpr int VP = R >= 64 ? 8 : 4;   // vectors per lane per step
-  constexpr int NS = R / VP;            // steps in the ring
-  static_assert(NS >= 2 && NS <= 12 && NS * VP == R, "ring geometry");
-  const long long n_mine = n_vec > lane ? (n_vec - 1 - lane) / 32 + 1 : 0;   // vectors of this lane
-  const long long n_steps = (n_mine + VP - 1) / VP;
-  auto off = [&](long long e) { return (e * 32 + lane) * 16; };
-  auto slot = [&](long long e) { return ring + (static_cast<uint32_t>(e % R) * 32u + lane) * 16u; };
-  auto issue = [&](long long st) {
-    if (st < n_steps) {
-#pragma unroll
-      for (int j = 0; j < VP; ++j) {
-        const long long e = st * VP + j;
-        if (e < n_mine) ptx::cp_async_16(slot(e), src + off(e));
-      }
-    }
-    ptx::cp_async_commit();
-  };
-  for (long long st = 0; st < NS - 1; ++st) issue(st);
-  for (long long st = 0; st < n_steps; ++st) {
-    issue(st + NS - 1);
-    ptx::cp_async_wait<NS - 1>();
-#pragma unroll
-    for (int j = 0; j < VP; ++j) {
-      const long long e = st * VP + j;
-      if (e < n_mine) {
-        const uint4 v = ptx::ld_shared_v4(slot(e));
-        if (nvls) ptx::multimem_st_v4(dst + off(e), v);
-        else ptx::st_global_v4(dst + off(e), v);
-      }
-    }
-  }
-  ptx::cp_async_wait<0>();
-}
-
-// Same copy with fan-out: every vector is loaded once and stored to all `n_dst` destinations
-// (the same offset of every peer's buffer), nearest ring distance first.
-template <int R>
-__device__ __forceinline__ void push_span_fanout(const char* src, char* const (&dst)[kMaxWorld],
-                                                 int n_dst, long long n_vec, uint32_t ring,
-                                                 int lane) {
-  constexpr int VP = R >= 64 ? 8 : 4;
-  constexpr int NS = R / VP;
-  static_assert(NS >= 2 && NS <= 12 && NS * VP == R, "ring geometry");
-  const long long n_mine = n_vec > lane ? (n_vec - 1 - lane) / 32 + 1 : 0;
-  const long long n_steps = (n_mine + VP - 1) / VP;
-  auto off = [&](long long e) { return (e * 32 + lane) * 16; };
-  auto slot = [&](long long e) { return ring + (static_cast<uint32_t>(e % R) * 32u + lane) * 16u; };
-  auto issue = [&](long long st) {
-    if (st < n_steps) {
-#pragma unroll
-      for (int j = 0; j < VP; ++j) {
-        const long long e = st * VP + j;
-        if (e < n_mine) ptx::cp_async_16(slot(e), src + off(e));
-      }
-    }
-    ptx::cp_async_commit();
-  };
-  for (long long st = 0; st < NS - 1; ++st) issue(st);
-  for (long long st = 0; st < n_steps; ++st) {
-    issue(st + NS - 1);
-    ptx::cp_async_wait<NS - 1>();
-#pragma unroll
-    for (int j = 0; j < VP; ++j) {
-      const long long e = st * VP + j;
-      if (e < n_mine) {
-        const uint4 v = ptx::ld_shared_v4(slot(e));
-        const long long o = off(e);
-#pragma unroll
-        for (int d = 0; d < kMaxWorld - 1; ++d)
-          if (d < n_dst) ptx::st_global_v4(dst[d] + o, v);
-      }
-    }
-  }
-  ptx::cp_async_wait<0>();
-}
-
-// Same copy, but every step (VP x 32 vectors = one contiguous range in both the ring and the
-// destination) leaves as ONE bulk store issued by lane 0: fewer, larger write requests on NVLink.
-template <int R>
-__device__ __forceinline__ void push_span_bulk(const char* src, char* dst, long long n_vec,
-                                               uint32_t ring, int lane) {
-  constexpr int VP = R >= 64 ? 8 : 4;
-  constexpr int NS = R / VP;
+struct PushRing {
+  static constexpr int VP = R >= 64 ? 8 : 4;   // vectors per lane per step
+  static constexpr int NS = R / VP;            // steps in the ring
+  static constexpr int kStepBytes = VP * 512;
   static_assert(NS >= 3 && NS <= 12 && NS * VP == R, "ring geometry");
-  const long long n_mine = n_vec > lane ? (n_vec - 1 - lane) / 32 + 1 : 0;
-  const long long n_steps = (n_vec + VP * 32 - 1) / (VP * 32);          // same for every lane
-  auto off = [&](long long e) { return (e * 32 + lane) * 16; };
-  auto slot = [&](long long e) { return ring + (static_cast<uint32_t>(e % R) * 32u + lane) * 16u; };
-  auto issue = [&](long long st) {
-    if (st < n_steps) {
+};
+
+// Loads of a push loop: `issue()` starts the next step's cp.async copies (or an empty group past
+// the end) and advances; the caller consumes step st after cp_async_wait<NS - 1 (or - 2)>.
+template <int R>
+struct PushLoader {
+  using G = PushRing<R>;
+  const char* src;     // lane's next source address
+  uint32_t ring_lane;  // ring base + lane * 16
+  int n_mine, n_steps, step, slot;
+  bool skip;
+  __device__ __forceinline__ PushLoader(const char* s, uint32_t ring, int n_vec, int lane, bool skip_)
+      : src(s + lane * 16), ring_lane(ring + lane * 16u),
+        n_mine(n_vec > lane ? (n_vec - 1 - lane) / 32 + 1 : 0), step(0), slot(0), skip(skip_) {
+    n_steps = (n_mine + G::VP - 1) / G::VP;
+  }
+  __device__ __forceinline__ uint32_t slot_addr(int ring_step) const {
+    return ring_lane + static_cast<uint32_t>(ring_step) * G::kStepBytes;
+  }
+  __device__ __forceinline__ void issue() {
+    if (step < n_steps && !skip) {
+      const uint32_t sb = slot_addr(slot);
+      const int left = n_mine - step * G::VP;
+      if (left >= G::VP) {
 #pragma unroll
-      for (int j = 0; j < VP; ++j) {
-        const long long e = st * VP + j;
-        if (e < n_mine) ptx::cp_async_16(slot(e), src + off(e));
+        for (int j = 0; j < G::VP; ++j) ptx::cp_async_16(sb + j * 512, src + j * 512);
+      } else {
+#pragma unroll
+        for (int j = 0; j < G::VP; ++j)
+          if (j < left) ptx::cp_async_16(sb + j * 512, src + j * 512);
       }
     }
     ptx::cp_async_commit();
-  };
+    src += G::kStepBytes;
+    ++step;
+    if (++slot == G::NS) slot = 0;
+  }
+};
+
+// AllGather item: copy `n_vec` 16-byte vectors from the own shard to the same offset of up to
+// kMaxWorld - 1 destinations (peers' buffers; or one destination: a peer or the multicast alias)
+// through the lane-private ring.  Every vector is loaded once.
+template <int R, int ND>
+__device__ __forceinline__ void push_span(const char* src, char* const (&dst_in)[ND], int n_dst,
+                                          int n_vec, bool nvls, uint32_t ring, int lane, int dbg) {
+  using G = PushRing<R>;
+  PushLoader<R> ld(src, ring, n_vec, lane, (dbg & 8) != 0);
+  char* dst[ND];
+#pragma unroll
+  for (int d = 0; d < ND; ++d) dst[d] = d < n_dst ? dst_in[d] + lane * 16 : nullptr;
+#pragma unroll 1
+  for (int i = 0; i < G::NS - 1; ++i) ld.issue();
+  int slot = 0;
+#pragma unroll 1
+  for (int st = 0; st < ld.n_steps; ++st) {
+    ld.issue();
+    ptx::cp_async_wait<G::NS - 1>();
+    const uint32_t sb = ld.slot_addr(slot);
+    const int left = ld.n_mine - st * G::VP;
+    uint4 v[G::VP];
+#pragma unroll
+    for (int j = 0; j < G::VP; ++j) v[j] = ptx::ld_shared_v4(sb + j * 512);
+    if (!(dbg & 16)) {
+#pragma unroll
+      for (int d = 0; d < ND; ++d) {
+        if (d >= n_dst) break;
+        if (left >= G::VP) {
+#pragma unroll
+          for (int j = 0; j < G::VP; ++j) {
+            if (nvls) ptx::multimem_st_v4(dst[d] + j * 512, v[j]);
+            else ptx::st_global_v4(dst[d] + j * 512, v[j]);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < G::VP; ++j) {
+            if (j >= left) break;
+            if (nvls) ptx::multimem_st_v4(dst[d] + j * 512, v[j]);
+            else ptx::st_global_v4(dst[d] + j * 512, v[j]);
+          }
+        }
+        dst[d] += G::kStepBytes;
+      }
+    }
+    if (++slot == G::NS) slot = 0;
+  }
+  ptx::cp_async_wait<0>();
+}
+
+// Same copy to one destination, but every step (VP x 32 vectors = one contiguous range in both
+// the ring and the destination) leaves as ONE bulk store issued by lane 0: fewer, larger write
+// requests on NVLink.
+template <int R>
+__device__ __forceinline__ void push_span_bulk(const char* src, char* dst, int n_vec,
+                                               uint32_t ring, int lane) {
+  using G = PushRing<R>;
+  PushLoader<R> ld(src, ring, n_vec, lane, false);
+  const int n_steps = (n_vec + G::VP * 32 - 1) / (G::VP * 32);          // same for every lane
   // The slots of step st are refilled by step st + NS - 2, issued after the bulk store of step
   // st - 1 ... so one ring step is always either being stored or free: NS - 2 steps in flight.
-  for (long long st = 0; st < NS - 2; ++st) issue(st);
-  for (long long st = 0; st < n_steps; ++st) {
+#pragma unroll 1
+  for (int i = 0; i < G::NS - 2; ++i) ld.issue();
+  int slot = 0;
+#pragma unroll 1
+  for (int st = 0; st < n_steps; ++st) {
     // the step about to be refilled was stored two iterations ago: its store must have read it
     if (lane == 0) ptx::bulk_wait_read<1>();
     __syncwarp();
-    issue(st + NS - 2);
-    ptx::cp_async_wait<NS - 2>();
+    ld.issue();
+    ptx::cp_async_wait<G::NS - 2>();
     ptx::fence_proxy_async();       // cp.async wrote the ring; the bulk store reads it
     __syncwarp();
     if (lane == 0) {
-      const long long first = st * VP * 32;
-      long long vecs = n_vec - first;
-      if (vecs > VP * 32) vecs = VP * 32;
-      ptx::bulk_s2g(dst + first * 16,
-                    ring + static_cast<uint32_t>((st * VP) % R) * 512u,
+      int vecs = n_vec - st * (G::VP * 32);
+      if (vecs > G::VP * 32) vecs = G::VP * 32;
+      ptx::bulk_s2g(dst, ring + static_cast<uint32_t>(slot) * G::kStepBytes,
                     static_cast<uint32_t>(vecs * 16));
       ptx::bulk_commit();
     }
+    dst += G::kStepBytes;
+    if (++slot == G::NS) slot = 0;
   }
   ptx::cp_async_wait<0>();
   if (lane == 0) {
@@ -541,65 +553,79 @@ struct ReduceSpan {
   const char* src[kMaxWorld];  // W copies of the same byte range
   char* dst[kMaxWorld];        // RS: dst[0] only; AR: every rank's output
   char* mc_dst;                // AR through NVSwitch multicast (or nullptr)
-  long long n_vec;             // 16-byte vectors in the range
+  int n_vec;                   // 16-byte vectors in the range
 };
 
 // Reduce item: sum W copies of a range.  Each lane owns every 32nd vector; the ring holds NS
-// steps of VP vectors x W copies, one cp.async commit group per step, NS-1 steps in flight.
-// fp32 accumulation in fixed rank order 0..W-1.
+// steps of VP vectors x WT copies (slot of (step, j, copy) = ((step % NS) * VP + j) * WT + copy),
+// one cp.async commit group per step, NS-1 steps in flight.  fp32 accumulation in fixed rank
+// order 0..W-1.
 template <int OP, int WT, int R>
 __device__ __forceinline__ void reduce_span(const ReduceSpan& sp, int W, uint32_t ring, int lane) {
   constexpr int VP = (R / (WT * 8)) >= 1 ? R / (WT * 8) : 1;   // vectors per lane per step
   constexpr int NS = R / (WT * VP);                             // steps in the ring
+  constexpr int kStepBytes = VP * WT * 512;
   static_assert(NS >= 2 && NS <= 12, "ring geometry");
-  const long long n_mine = sp.n_vec > lane ? (sp.n_vec - 1 - lane) / 32 + 1 : 0;
-  const long long n_steps = (n_mine + VP - 1) / VP;
-  auto slot = [&](long long i, int src) {
-    return ring + ((static_cast<uint32_t>(i % (NS * VP)) * WT + src) * 32u + lane) * 16u;
-  };
-  auto issue = [&](long long st) {
-    if (st < n_steps) {
+  const int n_mine = sp.n_vec > lane ? (sp.n_vec - 1 - lane) / 32 + 1 : 0;
+  const int n_steps = (n_mine + VP - 1) / VP;
+  const uint32_t ring_lane = ring + lane * 16u;
+  const char* src[WT];
+#pragma unroll
+  for (int c = 0; c < WT; ++c) src[c] = c < W ? sp.src[c] + lane * 16 : nullptr;
+  int i_step = 0, i_slot = 0;
+  auto issue = [&]() {
+    if (i_step < n_steps) {
+      const uint32_t sb = ring_lane + static_cast<uint32_t>(i_slot) * kStepBytes;
+      const int left = n_mine - i_step * VP;
 #pragma unroll
       for (int j = 0; j < VP; ++j) {
-        const long long i = st * VP + j;
-        if (i < n_mine) {
-          const long long v = i * 32 + lane;
+        if (j >= left) break;
 #pragma unroll
-          for (int src = 0; src < WT; ++src)
-            if (src < W) ptx::cp_async_16(slot(i, src), sp.src[src] + v * 16);
-        }
+        for (int c = 0; c < WT; ++c)
+          if (c < W) ptx::cp_async_16(sb + (j * WT + c) * 512, src[c] + j * 512);
       }
     }
     ptx::cp_async_commit();
+#pragma unroll
+    for (int c = 0; c < WT; ++c) src[c] += VP * 512;
+    ++i_step;
+    if (++i_slot == NS) i_slot = 0;
   };
-  for (long long st = 0; st < NS - 1; ++st) issue(st);
-  for (long long st = 0; st < n_steps; ++st) {
-    issue(st + NS - 1);
+  long long off = lane * 16;   // byte offset of the lane's vector j = 0 of the current step
+#pragma unroll 1
+  for (int i = 0; i < NS - 1; ++i) issue();
+  int slot = 0;
+#pragma unroll 1
+  for (int st = 0; st < n_steps; ++st) {
+    issue();
     ptx::cp_async_wait<NS - 1>();
+    const uint32_t sb = ring_lane + static_cast<uint32_t>(slot) * kStepBytes;
+    const int left = n_mine - st * VP;
 #pragma unroll
     for (int j = 0; j < VP; ++j) {
-      const long long i = st * VP + j;
-      if (i >= n_mine) continue;
-      const long long v = i * 32 + lane;
+      if (j >= left) break;
       float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-      for (int src = 0; src < WT; ++src)
-        if (src < W) accumulate_bf16x8(acc, ptx::ld_shared_v4(slot(i, src)));
+      for (int c = 0; c < WT; ++c)
+        if (c < W) accumulate_bf16x8(acc, ptx::ld_shared_v4(sb + (j * WT + c) * 512));
       uint4 r;
       r.x = ptx::pack_bf16x2(acc[0], acc[1]);
       r.y = ptx::pack_bf16x2(acc[2], acc[3]);
       r.z = ptx::pack_bf16x2(acc[4], acc[5]);
       r.w = ptx::pack_bf16x2(acc[6], acc[7]);
+      const long long o = off + j * 512;
       if (OP == OP_RS) {
-        ptx::st_global_v4(sp.dst[0] + v * 16, r);
+        ptx::st_global_v4(sp.dst[0] + o, r);
       } else if (sp.mc_dst != nullptr) {
-        ptx::multimem_st_v4(sp.mc_dst + v * 16, r);
+        ptx::multimem_st_v4(sp.mc_dst + o, r);
       } else {
 #pragma unroll
         for (int d = 0; d < WT; ++d)
-          if (d < W && sp.dst[d] != nullptr) ptx::st_global_v4(sp.dst[d] + v * 16, r);
+          if (d < W && sp.dst[d] != nullptr) ptx::st_global_v4(sp.dst[d] + o, r);
       }
     }
+    off += VP * 512;
+    if (++slot == NS) slot = 0;
   }
   ptx::cp_async_wait<0>();
 }
@@ -622,7 +648,8 @@ __device__ __forceinline__ void reduce_span_nvls(const char* mc_src, char* mc_ds
 // or when a wait expired.  `s_item` is a shared-memory word private to this warp.
 template <int OP, int R>
 __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring, WaitCtx& wc,
-                                                uint32_t epoch, volatile uint32_t* s_item) {
+                                                uint32_t epoch, volatile uint32_t* s_item,
+                                                volatile uint32_t* s_progress) {
   const Sched& s = p.sched;
   const int lane = threadIdx.x & 31;
   const int W = s.world;
@@ -656,7 +683,7 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
       const int r0 = g * (kBlockM / kGatherSub);
       int r1 = r0 + kBlockM / kGatherSub;
       if (r1 > rows_in_block) r1 = rows_in_block;
-      const long long n_vec = r1 > r0 ? (r1 - r0) * row_bytes / 16 : 0;
+      const int n_vec = r1 > r0 ? static_cast<int>((r1 - r0) * row_bytes / 16) : 0;
       const long long base = (static_cast<long long>(rowblock_row0(s, rowblock)) + r0) * row_bytes;
       const int dst_rank = (s.rank - d + W) % W;
       char* dst = nvls_ag ? static_cast<char*>(p.mc_data) : static_cast<char*>(p.peer_data[dst_rank]);
@@ -674,19 +701,33 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
         if (!__all_sync(0xffffffffu, ok)) return;
         for (int r = first; r <= last; ++r) entered_mask |= 1u << r;
       }
+      if (p.ag_lead_tiles > 0 && s_progress != nullptr) {
+        // Pacing: rows pushed long before their consumers need them only compete with the GEMM
+        // (here and at the receiver) for memory bandwidth and cache.  The receivers walk the same
+        // raster as this rank, so this CTA's own progress stands in for theirs: wait until the
+        // GEMM is within ag_lead_tiles of the raster group that consumes these rows.
+        const int pos = s.part_blocks + j * (W - 1) + (bcast_ag ? 0 : d - 1);
+        const int need = (pos / s.group_rows) * s.group_rows * s.Q - p.ag_lead_tiles;
+        if (need > 0) {
+          const bool ok = bounded_wait<true>(
+              wc, [&] { return static_cast<int>(*s_progress) >= need; }, ST_TIMEOUT_PACE, item, need);
+          if (!__all_sync(0xffffffffu, ok)) return;
+        }
+      }
       if (!(p.debug_flags & 1)) {
         if (bcast_ag && !nvls_ag) {
-          char* fan[kMaxWorld];
+          char* fan[kMaxWorld - 1];
 #pragma unroll
           for (int i = 0; i < kMaxWorld - 1; ++i)
             fan[i] = i < W - 1 ? static_cast<char*>(p.peer_data[(s.rank - 1 - i + W) % W]) + base
                                : nullptr;
-          fan[kMaxWorld - 1] = nullptr;
-          push_span_fanout<R>(local + base, fan, W - 1, n_vec, ring, lane);
+          push_span<R, kMaxWorld - 1>(local + base, fan, W - 1, n_vec, false, ring, lane,
+                                      p.debug_flags);
         } else if (p.push_bulk && !nvls_ag) {
           push_span_bulk<R>(local + base, dst + base, n_vec, ring, lane);
         } else {
-          push_span<R>(local + base, dst + base, n_vec, nvls_ag, ring, lane);
+          char* one[1] = {dst + base};
+          push_span<R, 1>(local + base, one, 1, n_vec, nvls_ag, ring, lane, p.debug_flags);
         }
       }
       __syncwarp();
@@ -758,7 +799,7 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
                            static_cast<char*>(p.mc_out) + base, n_vec, lane);
         } else {
           ReduceSpan sp;
-          sp.n_vec = n_vec;
+          sp.n_vec = static_cast<int>(n_vec);
           sp.mc_dst = (OP == OP_AR && p.use_nvls && !s.one_shot && p.mc_out != nullptr)
                           ? static_cast<char*>(p.mc_out) + base : nullptr;
 #pragma unroll
@@ -823,6 +864,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
   volatile uint32_t* s_tmem = s_words;       // TMEM base address
   volatile uint32_t* s_abort = s_words + 1;  // CTA-wide abort flag
   volatile uint32_t* s_epoch = s_words + 2;
+  volatile uint32_t* s_progress = s_words + 3;  // AllGather: tile the TMA producer has reached
   volatile uint32_t* s_item = s_words + 8;   // [8,16): one queue slot per warp
   const bool is_comm = static_cast<int>(blockIdx.x) < p.n_comm;
 
@@ -834,6 +876,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
 
   if (threadIdx.x == 0) {
     *s_abort = 0u;
+    *s_progress = 0u;
     uint32_t e = p.epoch_arg;
     // The epoch lives on the device (graph replays need no host state) unless the caller
     // supplies one (GEMM+AR and the multi-node style signatures pass a host epoch)
@@ -884,16 +927,17 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
   if (is_comm) {
     if (OP != OP_GEMM)
       exchange_worker<OP, kRingDedicated>(p, smem_base + warp * (kRingDedicated * 32 * 16), wc,
-                                          epoch, s_item + warp);
+                                          epoch, s_item + warp, nullptr);
   } else if (warp == 3) {
     if (OP != OP_GEMM) {
       if (p.ring_slots == kRingInCtaDeep)
-        exchange_worker<OP, kRingInCtaDeep>(p, xchg_ring, wc, epoch, s_item + warp);
+        exchange_worker<OP, kRingInCtaDeep>(p, xchg_ring, wc, epoch, s_item + warp, s_progress);
       else
-        exchange_worker<OP, kRingInCta>(p, xchg_ring, wc, epoch, s_item + warp);
+        exchange_worker<OP, kRingInCta>(p, xchg_ring, wc, epoch, s_item + warp, s_progress);
     }
   } else {
-    compute_roles<OP, CG>(&tma_a, &tma_b, p, smem_base, bar_base, epi_stage, *s_tmem, wc, epoch);
+    compute_roles<OP, CG>(&tma_a, &tma_b, p, smem_base, bar_base, epi_stage, *s_tmem, wc, epoch,
+                          s_progress);
   }
 
   // ---------------- teardown ----------------

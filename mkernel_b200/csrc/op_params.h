@@ -15,6 +15,8 @@ struct OpParams {
   int item_vecs;         // RS/AR: 16-byte vectors per exchange work item
   int n_items;           // exchange work items of this rank for this launch
   int push_bulk;         // AllGather push: leave each ring step as one TMA bulk store
+  int ag_lead_tiles;     // AllGather push pacing: an item may run this many tiles ahead of the
+                         // raster group that consumes its rows (0 = unpaced)
   int ag_fanout;         // AllGather push: one item loads a row group once, stores it to all peers
   int ring_slots;        // ring depth (16-byte slots per lane) of the in-CTA exchange warp
   int use_nvls;          // exchange through NVSwitch multicast addresses when available

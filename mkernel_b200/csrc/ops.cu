@@ -32,6 +32,7 @@ struct Options {
   long long group_rows = 0;
   long long use_nvls = 0;
   long long debug_flags = 0;
+  long long ag_lead = 0;     // AllGather push pacing, in quarter raster groups (0 = unpaced)
   long long ag_fanout = 0;   // AllGather push: load each row group once, store it to every peer
   long long push_bulk = 0;   // AllGather push through TMA bulk stores instead of LSU stores
   long long ar_one_shot = 0;  // GEMM+AR: 1 = every rank reduces all rows itself (no broadcast)
@@ -51,6 +52,7 @@ static long long* option_slot(const char* name) {
   if (!strcmp(name, "debug_flags")) return &g_opt.debug_flags;
   if (!strcmp(name, "push_bulk")) return &g_opt.push_bulk;
   if (!strcmp(name, "ag_fanout")) return &g_opt.ag_fanout;
+  if (!strcmp(name, "ag_lead")) return &g_opt.ag_lead;
   if (!strcmp(name, "ar_one_shot")) return &g_opt.ar_one_shot;
   return nullptr;
 }
@@ -362,6 +364,7 @@ static int run_op(const OpArgs& a, cudaStream_t stream) {
     p.debug_flags = (int)g_opt.debug_flags;
     p.push_bulk = (int)g_opt.push_bulk;
     p.ag_fanout = (int)g_opt.ag_fanout;
+    p.ag_lead_tiles = (int)(g_opt.ag_lead * pl.sched.group_rows * pl.sched.Q / 4);
   }
   if (a.world > 1 && a.op != OP_GEMM) {
     const int workers = (pl.grid - pl.n_comm) + 8 * pl.n_comm;

@@ -58,6 +58,7 @@ enum StatusCode : int {
   ST_TIMEOUT_EXIT = 4,      // exit handshake: a peer never reported completion
   ST_TIMEOUT_ENTRY = 5,     // entry barrier (prepare): a peer never arrived
   ST_TIMEOUT_COPY = 6,      // exchange role: a bulk copy never completed
+  ST_TIMEOUT_PACE = 7,      // AllGather push pacing: this CTA's GEMM never reached the tile
 };
 
 struct Sched {

@@ -112,3 +112,16 @@ def test_allgather_fanout():
         dict(op="ag", M=world * 1024, N=512, K=2048, seed=4, iters=2, max_rows=64),
     ]
     check(launch(world, cases, options={"ag_fanout": 1}))
+
+
+@pytest.mark.skipif(n_gpus() < 2, reason="needs at least 2 GPUs")
+def test_allgather_paced_push():
+    """Pacing the AllGather push against the GEMM's own progress changes timing only."""
+    world = min(n_gpus(), 8)
+    world = 1 << (world.bit_length() - 1)
+    cases = [
+        dict(op="ag", M=world * 1024, N=1024, K=1024, seed=5, iters=2, max_rows=64),
+        dict(op="ag", M=world * 72, N=512, K=200, seed=1, iters=2, max_rows=4096),
+        dict(op="ag", M=8192, N=3584, K=8192, seed=6, iters=2, max_rows=16),
+    ]
+    check(launch(world, cases, options={"ag_lead": 1}))
