@@ -202,7 +202,10 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
           const uint32_t a_dst = smem_base + stage * stage_sz;
           const uint32_t b_dst = a_dst + kBlockM * kBlockK * 2;
           const int nb0 = ti.n0 + crank * b_rows;   // first B row (C column) this CTA loads
-          if (CG == 1) {
+          if (p.debug_flags & 64) {
+            // diagnostics: no operand loads, the MMAs run on whatever the stage holds
+            if (crank == 0) ptx::mbar_arrive(bar(BAR_FULL + stage));
+          } else if (CG == 1) {
             ptx::mbar_expect_tx(bar(BAR_FULL + stage), stage_sz);
             ptx::tma_load_2d(a_dst, tma_a, bar(BAR_FULL + stage), kb * kBlockK, ti.row0);
             if (!p.b_mn_major) {
@@ -249,6 +252,7 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
           const uint32_t b_base = a_base + kBlockM * kBlockK * 2;
 #pragma unroll
           for (int k = 0; k < kBlockK / 16; ++k) {
+            if (p.debug_flags & 128) break;   // diagnostics: loads only, no MMAs
             // A: K-major, 128-byte swizzle: rows are 128 B apart, 8-row groups 1024 B apart;
             // a K step of 16 elements moves the start address by 32 B inside the swizzle row.
             const uint64_t a_desc = ptx::make_smem_desc_sw128(a_base + k * 32, 16, 1024);
@@ -663,13 +667,16 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
   const long long row_bytes = (OP == OP_AG ? static_cast<long long>(p.K) : static_cast<long long>(s.N)) * 2;
   char* const local = static_cast<char*>(p.peer_data[s.rank]);
   uint32_t entered_mask = 1u << s.rank;  // ranks known to have entered this launch
+  uint32_t next_item = 0;
+  if (lane == 0) next_item = atomicAdd(p.sync + SW_NEXT_ITEM, 1u);
+  (void)s_item;
 
   while (true) {
-    if (lane == 0) *s_item = atomicAdd(p.sync + SW_NEXT_ITEM, 1u);
-    __syncwarp();
-    const int item = static_cast<int>(*s_item);
-    __syncwarp();
+    // The queue is read one item ahead: the atomic for the next item is in flight while this
+    // one is processed, so its round trip to L2 is off the critical path.
+    const int item = static_cast<int>(__shfl_sync(0xffffffffu, next_item, 0));
     if (item >= p.n_items) break;
+    if (lane == 0) next_item = atomicAdd(p.sync + SW_NEXT_ITEM, 1u);
 
     if (OP == OP_AG) {
       // Item order: row-block j of the own shard goes to every receiver (nearest ring distance
