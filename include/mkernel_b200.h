@@ -156,7 +156,8 @@ int mk_op_status(const mk_symm_view* sync, uint32_t out4[4]);
 int mk_op_status_clear(const mk_symm_view* sync, void* stream);
 
 /* ---- options (process-wide): "wait_limit_ms" (device wait budget, default 4000),
- *      "n_comm" (dedicated exchange CTAs, -1 = heuristic), "block_n" (0 = heuristic), "group_rows",
+ *      "n_comm" (dedicated exchange CTAs, -1 = heuristic), "block_n" (0 = heuristic), "group_rows" / "group_cols"
+ *      (raster group in row / column blocks, 0 = heuristic; column groups apply on one GPU only),
  *      "use_nvls" (0/1: exchange through NVSwitch multicast when the buffers have an alias),
  *      "cta_pair" (0/1, default 1: two-SM MMA over CTA pairs when the shape allows),
  *      "ar_one_shot" (GEMM+AR: 0 = two-shot, owners reduce and broadcast; 1 = one-shot, every
@@ -164,7 +165,7 @@ int mk_op_status_clear(const mk_symm_view* sync, void* stream);
  *      receiver, 1 = an item loads its rows once and stores them to every peer), "push_bulk"
  *      (AllGather push through bulk shared-to-global stores), "ag_lead" (AllGather push pacing:
  *      rows are pushed at most this many quarter raster groups before the GEMM reaches the group
- *      that consumes them; 0 = push as fast as possible), "debug_flags" (timing diagnostics;
+ *      that consumes them; default 6, 0 = push as fast as possible), "debug_flags" (timing diagnostics;
  *      results undefined).  The environment variable MKERNEL_B200_OPTIONS="name=value,..." sets
  *      start-up defaults when the library is loaded. */
 int mk_set_option(const char* name, long long value);
@@ -175,6 +176,7 @@ typedef struct mk_plan {
   int block_n, stages, n_comm, grid, smem_bytes;
   int row_blocks, col_blocks, k_blocks, part_rows, part_blocks, interleave, group_rows;
   long long sync_words;
+  int group_cols;
 } mk_plan;
 /* Launch plan for op (0 GEMM, 1 AG, 2 RS, 3 AR) without touching a device; num_sms <= 0 means
  * 148. */
@@ -183,7 +185,7 @@ int mk_plan_op(int op, int rank, int world, int M, int N, int K, int b_layout, i
 /* Tile visiting order of a compute CTA set: writes row0/rows/col0 per tile, returns tile count
  * (or a negative status).  `cap` is the capacity of each output array. */
 int mk_sched_tiles(int op, int rank, int world, int M, int N, int block_n, int group_rows,
-                   int* row0, int* rows, int* col0, int* rowblock, int cap);
+                   int group_cols, int* row0, int* rows, int* col0, int* rowblock, int cap);
 /* Rows [row0,row1) that owner `owner` reduces for its k-th item; returns number of items. */
 int mk_sched_owner_items(int op, int world, int M, int N, int block_n, int owner, int* row0,
                          int* row1, int cap);

@@ -54,7 +54,7 @@ class Plan(Structure):
     _fields_ = [(n, c_int) for n in (
         "block_n", "stages", "n_comm", "grid", "smem_bytes", "row_blocks", "col_blocks",
         "k_blocks", "part_rows", "part_blocks", "interleave", "group_rows")] + [
-        ("sync_words", c_longlong)]
+        ("sync_words", c_longlong), ("group_cols", c_int)]
 
 
 LIB_PATH = Path(__file__).resolve().parent / "libmkernel_b200.so"
@@ -96,7 +96,7 @@ _SIGNATURES = {
     "mk_get_option": (c_longlong, [c_char_p]),
     "mk_plan_op": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                            POINTER(Plan)]),
-    "mk_sched_tiles": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, POINTER(c_int),
+    "mk_sched_tiles": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, POINTER(c_int),
                                POINTER(c_int), POINTER(c_int), POINTER(c_int), c_int]),
     "mk_sched_owner_items": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, POINTER(c_int),
                                      POINTER(c_int), c_int]),
@@ -147,12 +147,12 @@ def plan_op(op: int, rank: int, world: int, M: int, N: int, K: int, b_layout: in
 
 
 def sched_tiles(op: int, rank: int, world: int, M: int, N: int, block_n: int,
-                group_rows: int = 8):
+                group_rows: int = 8, group_cols: int = 0):
     """[(row0, rows, col0, rowblock)] in the order the compute CTAs visit the tiles."""
-    n = check(lib().mk_sched_tiles(op, rank, world, M, N, block_n, group_rows, None, None, None,
-                                   None, 0))
+    n = check(lib().mk_sched_tiles(op, rank, world, M, N, block_n, group_rows, group_cols, None,
+                                   None, None, None, 0))
     arr = [(c_int * n)() for _ in range(4)]
-    check(lib().mk_sched_tiles(op, rank, world, M, N, block_n, group_rows, *arr, n))
+    check(lib().mk_sched_tiles(op, rank, world, M, N, block_n, group_rows, group_cols, *arr, n))
     return list(zip(*(list(a) for a in arr)))
 
 

@@ -104,6 +104,12 @@ __device__ __forceinline__ bool bounded_wait(const WaitCtx& c, Pred pred, int co
   return slow_wait<kSleep>(c, pred, code, d0, d1);
 }
 
+// "This rank has entered (or left) launch e" slots only move forward: a peer that is already one
+// launch ahead has certainly passed launch `epoch` (wrap-safe comparison).
+__device__ __forceinline__ bool reached(uint32_t flag, uint32_t epoch) {
+  return static_cast<int32_t>(flag - epoch) >= 0;
+}
+
 __device__ __forceinline__ bool wait_mbar(const WaitCtx& c, uint32_t bar, uint32_t parity,
                                           uint32_t d0) {
   return bounded_wait<false>(c, [&] { return ptx::mbar_try_wait(bar, parity); },
@@ -331,7 +337,7 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
         for (int o = lo; o <= hi && ok; ++o) {
           if (entered_mask & (1u << o)) continue;
           const uint32_t* f = p.sync + SW_ENTRY + o;
-          ok = bounded_wait<true>(wc, [&] { return ptx::ld_acquire_sys(f) == epoch; },
+          ok = bounded_wait<true>(wc, [&] { return reached(ptx::ld_acquire_sys(f), epoch); },
                                   ST_TIMEOUT_ENTRY, o, epoch);
           entered_mask |= 1u << o;
         }
@@ -702,7 +708,7 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
         for (int r = first + lane; r <= last && ok; r += 32) {
           if (entered_mask & (1u << r)) continue;
           const uint32_t* f = p.sync + SW_ENTRY + r;
-          ok = bounded_wait<true>(wc, [&] { return ptx::ld_acquire_sys(f) == epoch; },
+          ok = bounded_wait<true>(wc, [&] { return reached(ptx::ld_acquire_sys(f), epoch); },
                                   ST_TIMEOUT_ENTRY, r, epoch);
         }
         if (!__all_sync(0xffffffffu, ok)) return;
@@ -979,7 +985,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
     if (OP == OP_AR && s.world > 1 && *s_abort == 0u) {
       for (int r = 0; r < s.world; ++r) {
         const uint32_t* f = p.sync + SW_EXIT + r;
-        if (!bounded_wait<true>(wc, [&] { return ptx::ld_acquire_sys(f) == epoch; },
+        if (!bounded_wait<true>(wc, [&] { return reached(ptx::ld_acquire_sys(f), epoch); },
                                 ST_TIMEOUT_EXIT, r, epoch))
           break;
       }

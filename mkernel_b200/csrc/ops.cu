@@ -30,9 +30,13 @@ struct Options {
   long long n_comm = -1;   // dedicated exchange CTAs; -1 = heuristic
   long long block_n = 0;
   long long group_rows = 0;
+  long long group_cols = 0;   // raster group width in column blocks; 0 = heuristic
   long long use_nvls = 0;
   long long debug_flags = 0;
-  long long ag_lead = 0;     // AllGather push pacing, in quarter raster groups (0 = unpaced)
+  // AllGather push pacing, in quarter raster groups (0 = unpaced).  Measured on B200: unpaced
+  // pushes arrive long before they are consumed and slow the GEMM on both sides (W=8: 0.504 ms
+  // unpaced, 0.445 at 4..8, 0.624 at 2 which starves the consumers; W=2: 0.418 / 0.404 / 0.396).
+  long long ag_lead = 6;
   long long ag_fanout = 0;   // AllGather push: load each row group once, store it to every peer
   long long push_bulk = 0;   // AllGather push through TMA bulk stores instead of LSU stores
   long long ar_one_shot = 0;  // GEMM+AR: 1 = every rank reduces all rows itself (no broadcast)
@@ -47,6 +51,7 @@ static long long* option_slot(const char* name) {
   if (!strcmp(name, "n_comm")) return &g_opt.n_comm;
   if (!strcmp(name, "block_n")) return &g_opt.block_n;
   if (!strcmp(name, "group_rows")) return &g_opt.group_rows;
+  if (!strcmp(name, "group_cols")) return &g_opt.group_cols;
   if (!strcmp(name, "use_nvls")) return &g_opt.use_nvls;
   if (!strcmp(name, "cta_pair")) return &g_opt.cta_pair;
   if (!strcmp(name, "debug_flags")) return &g_opt.debug_flags;
@@ -161,7 +166,7 @@ static int make_plan(int op, int rank, int world, int M, int N, int K, int b_lay
     }
   }
   Plan pl;
-  pl.sched = make_sched(op, rank, world, M, N, bn, group);
+  pl.sched = make_sched(op, rank, world, M, N, bn, group, (int)o.group_cols);
   if (op == OP_AR && world > 1 && o.ar_one_shot != 0) {
     pl.sched.one_shot = 1;
     pl.sched.interleave = 0;
@@ -687,14 +692,15 @@ int mk_plan_op(int op, int rank, int world, int M, int N, int K, int b_layout, i
   out->interleave = pl.sched.interleave;
   out->group_rows = pl.sched.group_rows;
   out->sync_words = sync_words_needed(pl.sched);
+  out->group_cols = pl.sched.group_cols;
   return MK_OK;
 }
 
 int mk_sched_tiles(int op, int rank, int world, int M, int N, int block_n, int group_rows,
-                   int* row0, int* rows, int* col0, int* rowblock, int cap) {
+                   int group_cols, int* row0, int* rows, int* col0, int* rowblock, int cap) {
   if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world || block_n < 8 || M < 1 || N < 1)
     return set_error(MK_ERR_INVALID, "mk_sched_tiles: bad arguments");
-  const Sched s = make_sched(op, rank, world, M, N, block_n, group_rows);
+  const Sched s = make_sched(op, rank, world, M, N, block_n, group_rows, group_cols);
   const int total = s.P * s.Q;
   for (int t = 0; t < total && t < cap; ++t) {
     int rb, q;

@@ -71,13 +71,15 @@ struct Sched {
   int P;           // row-blocks: AG: world*part_blocks, else ceil(M/128)
   int Q;           // column blocks: ceil(N / block_n)
   int group_rows;  // raster group height in row-blocks
+  int group_cols;  // raster group width in column blocks (Q = the whole width)
   int interleave;  // RS/AR: 1 when part_rows % 128 == 0 (owner-interleaved order)
   int one_shot;    // AR only: every rank reduces every row for itself (no result broadcast)
 };
 
 MKB_HD int ceil_div(int a, int b) { return (a + b - 1) / b; }
 
-MKB_HD Sched make_sched(int op, int rank, int world, int M, int N, int block_n, int group_rows) {
+MKB_HD Sched make_sched(int op, int rank, int world, int M, int N, int block_n, int group_rows,
+                        int group_cols = 0) {
   Sched s;
   s.op = op; s.rank = rank; s.world = world; s.M = M; s.N = N; s.block_n = block_n;
   if (op == OP_AG) s.part_rows = M / world;              // rows of one gathered shard
@@ -88,6 +90,9 @@ MKB_HD Sched make_sched(int op, int rank, int world, int M, int N, int block_n, 
   s.P = (op == OP_AG) ? world * s.part_blocks : ceil_div(M, kBlockM);
   s.Q = ceil_div(N, block_n);
   s.group_rows = group_rows < 1 ? 1 : group_rows;
+  // Column grouping makes a second pass over all rows, which the row-ordered exchanges (rows
+  // consumed as they arrive, owners served round by round) cannot afford: one GPU only.
+  s.group_cols = (group_cols < 1 || group_cols > s.Q || world > 1) ? s.Q : group_cols;
   s.interleave = ((op == OP_RS || op == OP_AR) && world > 1 && (s.part_rows % kBlockM) == 0 &&
                   s.part_blocks * world == s.P) ? 1 : 0;
   s.one_shot = 0;
@@ -119,13 +124,19 @@ MKB_HD int order_to_rowblock(const Sched& s, int i) {
 // Linear tile index -> (row-block id, column block).  Tiles are rastered in groups of
 // group_rows row-blocks; inside a group the row-block index runs fastest so the CTAs working at
 // the same time share a few A row-blocks and a contiguous range of B column blocks in L2.
+// With group_cols < Q the raster is two-level: column groups outermost (all rows pass once per
+// column group, so a group's slice of B plus one row group of A is what L2 has to hold).
 MKB_HD void tile_to_coord(const Sched& s, int t, int* rowblock, int* q) {
-  const int per_group = s.group_rows * s.Q;
-  const int g = t / per_group, r = t % per_group;
+  const int cg = t / (s.P * s.group_cols);            // full column groups precede a partial one
+  const int q0 = cg * s.group_cols;
+  const int cols_here = (s.Q - q0) < s.group_cols ? (s.Q - q0) : s.group_cols;
+  const int tt = t - cg * s.P * s.group_cols;
+  const int per_group = s.group_rows * cols_here;
+  const int g = tt / per_group, r = tt % per_group;
   const int first = g * s.group_rows;
   const int rows_here = (s.P - first) < s.group_rows ? (s.P - first) : s.group_rows;
   const int i = first + r % rows_here;
-  *q = r / rows_here;
+  *q = q0 + r / rows_here;
   *rowblock = order_to_rowblock(s, i);
 }
 

@@ -115,3 +115,25 @@ def test_block_width_avoids_wave_quantisation():
     # decode-shaped all-reduce: every tile gets its own CTA
     p = _lib.plan_op(OP_AR, 0, 8, 128, 8192, 1024, 1, 148)
     assert p.row_blocks * p.col_blocks <= p.grid - p.n_comm
+
+
+@pytest.mark.parametrize("M,N,bn,gr,gc", [(8192, 3584, 256, 12, 7), (8192, 3584, 256, 8, 4),
+                                          (1000, 1000, 96, 6, 3), (8192, 28672, 256, 12, 16),
+                                          (384, 8192, 128, 2, 5)])
+def test_two_level_raster_covers_every_tile_once_and_keeps_pairs_in_one_column(M, N, bn, gr, gc):
+    """Column groups outermost, row groups inside, row-block fastest: every tile once; with an
+    even number of row-blocks and an even group height tiles 2i and 2i+1 share a column block
+    (what a CTA pair needs); a column group is finished before the next one starts."""
+    tiles = _lib.sched_tiles(OP_GEMM, 0, 1, M, N, bn, gr, gc)
+    P, Q = -(-M // 128), -(-N // bn)
+    assert len(tiles) == P * Q
+    assert len({(r0, c0) for r0, _, c0, _ in tiles}) == P * Q
+    if P % 2 == 0 and gr % 2 == 0:
+        for i in range(0, len(tiles), 2):
+            assert tiles[i][2] == tiles[i + 1][2] and tiles[i][0] != tiles[i + 1][0]
+    groups = [c0 // bn // gc for _, _, c0, _ in tiles]
+    assert groups == sorted(groups)
+    # more than one GPU: the exchanges are row-ordered, column grouping is ignored
+    a = _lib.sched_tiles(OP_AG, 1, 4, 8192, 3584, 256, 8, 4)
+    b = _lib.sched_tiles(OP_AG, 1, 4, 8192, 3584, 256, 8, 0)
+    assert a == b
