@@ -125,3 +125,19 @@ def test_allgather_paced_push():
         dict(op="ag", M=8192, N=3584, K=8192, seed=6, iters=2, max_rows=16),
     ]
     check(launch(world, cases, options={"ag_lead": 1}))
+
+
+@pytest.mark.skipif(n_gpus() < 2, reason="needs at least 2 GPUs")
+def test_nvswitch_multicast_paths():
+    """Exchange through the multicast alias (multimem.st pushes for AllGather, multimem.ld_reduce +
+    multimem.st for AllReduce) gives the same results; buffers without an alias (multicast not
+    supported) fall back to peer loads and stores."""
+    world = min(n_gpus(), 8)
+    world = 1 << (world.bit_length() - 1)
+    cases = [
+        dict(op="ag", M=world * 256, N=264, K=1024, seed=1, iters=2, max_rows=4096, multicast=True),
+        dict(op="ag", M=8192, N=3584, K=8192, seed=6, iters=2, max_rows=16, multicast=True),
+        dict(op="ar", M=128, N=8192, K=1024, seed=3, iters=3, max_rows=128, multicast=True),
+        dict(op="ar", M=200, N=264, K=136, seed=7, iters=2, max_rows=4096, multicast=True),
+    ]
+    check(launch(world, cases, options={"use_nvls": 1}))
