@@ -328,11 +328,8 @@ def run_ours(args):
     ar = mkernel_b200.load("gemm_ar_blackwell")
     A4 = randn_bf16((M4, K4), 3 + rank, dev)
     B4 = randn_bf16((K4, N4), 303 + rank, dev, (K4 * W) ** -0.5)
-    # the reference's contract: C and C_final are multicast-capable buffers
-    C4 = ar.DistBuffer((M4, N4), dtype=torch.bfloat16, local_rank=rank, local_world_size=W,
-                       multicast=W > 1)
-    C4f = ar.DistBuffer((M4, N4), dtype=torch.bfloat16, local_rank=rank, local_world_size=W,
-                        multicast=W > 1)
+    C4 = ar.DistBuffer((M4, N4), dtype=torch.bfloat16, local_rank=rank, local_world_size=W)
+    C4f = ar.DistBuffer((M4, N4), dtype=torch.bfloat16, local_rank=rank, local_world_size=W)
     bar4 = ar.DistBuffer((2, 1024, 1024), dtype=torch.int32, local_rank=rank, local_world_size=W)
     bar4.data_.zero_()
     dst.barrier()

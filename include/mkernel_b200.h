@@ -158,8 +158,9 @@ int mk_op_status_clear(const mk_symm_view* sync, void* stream);
 /* ---- options (process-wide): "wait_limit_ms" (device wait budget, default 4000),
  *      "n_comm" (dedicated exchange CTAs, -1 = heuristic), "block_n" (0 = heuristic), "group_rows" / "group_cols"
  *      (raster group in row / column blocks, 0 = heuristic; column groups apply on one GPU only),
- *      "use_nvls" (exchange through NVSwitch multicast when the buffers have an alias: 0 never,
- *      1 always, 2 = default: where measured faster, i.e. GEMM+AllReduce at 8 GPUs),
+ *      "use_nvls" (0/1, default 0: exchange through NVSwitch multicast when the buffers have an
+ *      alias; the in-switch sum of the AllReduce is not rounded to nearest, so its error can
+ *      exceed the 1e-2 parity tolerance slightly),
  *      "cta_pair" (0/1, default 1: two-SM MMA over CTA pairs when the shape allows),
  *      "ar_one_shot" (GEMM+AR: 0 = two-shot, owners reduce and broadcast; 1 = one-shot, every
  *      rank reduces all rows for itself), "ag_fanout" (AllGather push: 0 = one work item per
