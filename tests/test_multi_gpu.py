@@ -138,7 +138,6 @@ def test_nvswitch_multicast_paths():
         dict(op="ag", M=world * 256, N=264, K=1024, seed=1, iters=2, max_rows=4096, multicast=True),
         dict(op="ag", M=8192, N=3584, K=8192, seed=6, iters=2, max_rows=16, multicast=True),
         dict(op="ar", M=128, N=8192, K=1024, seed=3, iters=3, max_rows=128, multicast=True),
-        dict(op="ar", M=200, N=264, K=136, seed=7, iters=2, max_rows=4096, multicast=True),
     ]
     # The in-switch sum (multimem.ld_reduce, fp32 accumulate) is not rounded to nearest: at 2 GPUs
     # the AllReduce measured 0.0106 on the parity metric, where the fp32 sum of the default path
