@@ -502,6 +502,77 @@ def run_sweep(args):
         dst.dist.destroy_process_group()
 
 
+def run_case(args):
+    """One operator a few times on one GPU (world size 1, empty exchange step) with seeded
+    synthetic operands: the small, bounded case to put under a profiler, e.g.
+    ``ncu -k regex:fused_gemm_kernel ... python bench.py --case ag --m 4096 --n 3584 --k 8192``.
+    --with-cublas also runs torch.mm (cuBLAS) on the same operands so that one capture holds
+    both kernels.  Prints a plain text line, not the bench JSON."""
+    import mkernel_b200
+    from mkernel_b200 import _lib, ops
+
+    M, N, K = args.m, args.n, args.k
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(0)
+    g = torch.Generator(device=dev).manual_seed(1)
+    A = torch.randn((M, K), device=dev, generator=g).to(torch.bfloat16)
+    B_nk = (torch.randn((N, K), device=dev, generator=g) * K ** -0.5).to(torch.bfloat16)
+    if args.block_n:
+        _lib.set_option("block_n", args.block_n)
+    if args.cta_pair is not None:
+        _lib.set_option("cta_pair", args.cta_pair)
+    if args.case == "gemm":
+        C = torch.empty((M, N), device=dev, dtype=torch.bfloat16)
+        run = lambda i: ops.gemm_bf16(A, B_nk, C)
+    elif args.case == "ag":
+        mod = mkernel_b200.load("ag_gemm_warp_specialized")
+        Ab = mod.DistBuffer((1, M, K), dtype=torch.bfloat16, local_rank=0, local_world_size=1)
+        Ab.data_[0].copy_(A)
+        ready = mod.DistBuffer((mod.ag_gemm_warp_specialized_ready_words,), dtype=torch.int32,
+                               local_rank=0, local_world_size=1)
+        ready.data_.zero_()
+        C = torch.empty((1, M, N), device=dev, dtype=torch.bfloat16)
+
+        def run(i):
+            mod.ag_gemm_warp_specialized_prepare(ready, M, N)
+            mod.ag_gemm_warp_specialized_launch(Ab, ready, B_nk, C)
+    elif args.case == "rs":
+        mod = mkernel_b200.load("gemm_rs_blackwell")
+        Cb = mod.DistBuffer((M, N), dtype=torch.bfloat16, local_rank=0, local_world_size=1)
+        sync = mod.DistBuffer(mod.gemm_rs_blackwell_sync_shape, dtype=torch.int32, local_rank=0,
+                              local_world_size=1)
+        mod.gemm_rs_blackwell_prepare(A, B_nk, Cb, sync)
+        run = lambda i: mod.gemm_rs_blackwell_launch(A, B_nk, Cb, sync)
+    else:
+        mod = mkernel_b200.load("gemm_ar_blackwell")
+        B_kn = B_nk.t().contiguous()
+        Cb = mod.DistBuffer((M, N), dtype=torch.bfloat16, local_rank=0, local_world_size=1)
+        Cf = mod.DistBuffer((M, N), dtype=torch.bfloat16, local_rank=0, local_world_size=1)
+        bar = mod.DistBuffer((2, 1024, 1024), dtype=torch.int32, local_rank=0, local_world_size=1)
+        bar.data_.zero_()
+        run = lambda i: mod.gemm_ar_intranode_blackwell(A, B_kn, Cb, bar, Cf, i + 1)
+
+    def timed(fn, iters, warmup):
+        for i in range(warmup):
+            fn(i)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(iters):
+            fn(warmup + i)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / iters
+
+    ms = timed(run, args.iters, args.case_warmup)
+    print(f"case={args.case} M={M} N={N} K={K}: {ms:.4f} ms/iter, "
+          f"{2.0 * M * N * K / ms / 1e9:.1f} TFLOP/s")
+    if args.with_cublas:
+        C2 = torch.empty((M, N), device=dev, dtype=torch.bfloat16)
+        ms = timed(lambda i: torch.mm(A, B_nk.t(), out=C2), args.iters, args.case_warmup)
+        print(f"cublas M={M} N={N} K={K}: {ms:.4f} ms/iter, {2.0 * M * N * K / ms / 1e9:.1f} TFLOP/s")
+
+
 def plan_summary(_lib, W, rank):
     out = {}
     for name, op, cfg, layout in (("ag_gemm", _lib.OP_AG, CFG2, 0), ("gemm_rs", _lib.OP_RS, CFG3, 0),
@@ -609,8 +680,20 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--sweep", action="store_true",
                     help="time the M x world-size sweep (BASELINE config 5) instead of the headline")
+    ap.add_argument("--case", choices=["gemm", "ag", "rs", "ar"],
+                    help="run one operator on one GPU a few times (a small case for a profiler)")
+    ap.add_argument("--m", type=int, default=4096)
+    ap.add_argument("--n", type=int, default=3584)
+    ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--iters", type=int, default=3)
+    ap.add_argument("--case-warmup", type=int, default=2)
+    ap.add_argument("--block-n", type=int, default=0)
+    ap.add_argument("--cta-pair", type=int, default=None)
+    ap.add_argument("--with-cublas", action="store_true")
     args = ap.parse_args()
-    if args.sweep:
+    if args.case:
+        run_case(args)
+    elif args.sweep:
         run_sweep(args)
     elif args.impl == "reference":
         run_reference(args)

@@ -8,6 +8,7 @@ Errors map the way the reference's do at its pybind boundary: argument problems 
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import (POINTER, Structure, c_char_p, c_int, c_longlong, c_size_t, c_uint32,
                     c_void_p)
 from pathlib import Path
@@ -29,6 +30,7 @@ STATUS_NAMES = {
     4: "a peer never reported completion (exit handshake)",
     5: "a peer never reached the entry barrier",
     6: "a bulk copy never completed",
+    7: "AllGather push pacing: this CTA's GEMM never reached the awaited tile",
 }
 
 
@@ -57,7 +59,11 @@ class Plan(Structure):
         ("sync_words", c_longlong), ("group_cols", c_int)]
 
 
-LIB_PATH = Path(__file__).resolve().parent / "libmkernel_b200.so"
+# MKERNEL_B200_LIB selects another build of the same library (the diagnostics build made by
+# `python -m mkernel_b200.build --diag`); the reference has the same kind of override for where
+# its .so files are taken from (python/load_module.py:19-74, MKERNEL_LOCAL_SO_DIR).
+LIB_PATH = Path(os.environ.get("MKERNEL_B200_LIB") or
+                Path(__file__).resolve().parent / "libmkernel_b200.so")
 _lib = None
 
 _SIGNATURES = {

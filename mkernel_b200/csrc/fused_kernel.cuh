@@ -35,6 +35,19 @@
 
 namespace mkb {
 
+// Timing diagnostics (skipping loads, MMAs or data movement; per-role wait counters) exist only
+// in builds made with -DMKB_DIAG; the default build compiles every such branch away.
+#ifdef MKB_DIAG
+constexpr bool kDiag = true;
+#else
+constexpr bool kDiag = false;
+#endif
+__device__ __forceinline__ bool diag(const OpParams& p, int bit) {
+  return kDiag && (p.debug_flags & bit) != 0;
+}
+// Cycle counter read used only by the diagnostics build.
+__device__ __forceinline__ long long diag_clock(bool on) { return on ? clock64() : 0ll; }
+
 // Barrier slots inside the CTA's barrier block (8 bytes each).
 enum BarSlot : int {
   BAR_FULL = 0,      // [0,8)   operand stage filled by TMA           (compute CTAs)
@@ -119,7 +132,7 @@ __device__ __forceinline__ bool wait_mbar(const WaitCtx& c, uint32_t bar, uint32
 // Timing diagnostics (debug_flags & 4): low 32 bits of %globaltimer at a few protocol events,
 // written to the otherwise unused sync words [24, 32).
 __device__ __forceinline__ void stamp(const OpParams& p, int slot) {
-  if ((p.debug_flags & 4) && p.sync != nullptr)
+  if (diag(p, 4) && p.sync != nullptr)
     p.sync[24 + slot] = static_cast<uint32_t>(global_timer_ns());
 }
 
@@ -139,7 +152,7 @@ __device__ __forceinline__ TileInfo tile_info(const Sched& s, int t) {
 template <int OP>
 __device__ __forceinline__ __nv_bfloat16* output_row(const OpParams& p, int grow) {
   const Sched& s = p.sched;
-  if (OP == OP_RS && s.world > 1 && !(p.debug_flags & 2)) {
+  if (OP == OP_RS && s.world > 1 && !diag(p, 2)) {
     // ReduceScatter: the row belongs to owner o and goes straight into o's buffer, into the
     // slab reserved for this (producing) rank.  Remote when o != rank: posted NVLink writes.
     int o = grow / s.part_rows;
@@ -174,7 +187,7 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
   // First tile of this CTA; the stride is n_comp for both modes (pairs step by n_comp / 2).
   const int cta = CG == 2 ? (((static_cast<int>(blockIdx.x) - p.n_comm) & ~1) + crank)
                           : static_cast<int>(blockIdx.x) - p.n_comm;
-  const int total = (p.debug_flags & 32) ? 0 : s.P * s.Q;   // diagnostics: exchange only
+  const int total = diag(p, 32) ? 0 : s.P * s.Q;   // diagnostics: exchange only
   const int bn = s.block_n;
   const int b_rows = bn / CG;                         // B rows (columns of C) this CTA loads
   const int stage_sz = kBlockM * kBlockK * 2 + b_rows * kBlockK * 2;
@@ -182,13 +195,28 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
   // Barriers the pair shares live in the leader CTA.
   auto lead = [&](int slot) { return CG == 2 ? ptx::map_to_cta(bar(slot), 0) : bar(slot); };
   constexpr bool kSignals = (OP == OP_RS || OP == OP_AR);
+  // Diagnostics build: p.trace set = coarse counters (kernel and MMA-loop cycles); flag 256 adds
+  // a cycle-counter read around every wait, which itself slows the MMA issue loop.
+  const bool trc = kDiag && p.trace != nullptr;
+  const bool tr = trc && diag(p, 256);
 
   if (warp == 0) {
     // ---------------- TMA producer ----------------
+    // Everything the per-k-block loop needs is copied into registers first: the parameter block
+    // is read through a reference, and every barrier / TMA instruction below is a compiler
+    // memory barrier, so a field left in the block would be re-read once per use.
     wc.where = (blockIdx.x << 8) | 0u;
+    const int k_blocks = p.k_blocks, stages = p.stages;
+    const bool b_mn = p.b_mn_major != 0;
+    const bool no_loads = diag(p, 64), idle = diag(p, 1024);
+    const uint32_t full0 = CG == 2 ? lead(BAR_FULL) : bar(BAR_FULL);   // + 8 * stage
+    const uint32_t full0_local = bar(BAR_FULL), empty0 = bar(BAR_EMPTY);
+    const uint32_t tx_bytes = static_cast<uint32_t>(CG * stage_sz);
+    const int b_panels = b_rows / 64;
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
+    long long tr_empty = 0, tr_gather = 0;
     for (int t = cta; t < total && ok; t += n_comp) {
       const TileInfo ti = tile_info(s, t);
       if (OP == OP_AG && lane == 0) *s_progress = static_cast<uint32_t>(t);
@@ -196,99 +224,128 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
         // Rows of a remote shard: wait until the sender has landed all 4-row groups here.
         static_assert(kGatherSub == 32, "one group flag per producer lane");
         const uint32_t* f = p.sync + SW_FLAGS + gather_flag_index(ti.rowblock, lane);
+        const long long c0 = diag_clock(tr);
         const bool mine = bounded_wait<true>(wc, [&] { return ptx::ld_acquire_sys(f) == epoch; },
                                              ST_TIMEOUT_GATHER, ti.rowblock, lane);
+        tr_gather += diag_clock(tr) - c0;
         ok = __all_sync(0xffffffffu, mine);
         ptx::fence_proxy_async();  // rows stored by a peer GPU are about to be read by TMA
         if (!ok) break;
       }
-      if (lane == 0) {
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!wait_mbar(wc, bar(BAR_EMPTY + stage), phase ^ 1u, 0x100u + stage)) { ok = false; break; }
+      if (lane == 0 && !idle) {
+        const int row0 = ti.row0;
+        const int nb0 = ti.n0 + crank * b_rows;   // first B row (C column) this CTA loads
+        int kx = 0;                                // element offset of the k-block
+        for (int kb = 0; kb < k_blocks; ++kb, kx += kBlockK) {
+          const long long c0 = diag_clock(tr);
+          if (!wait_mbar(wc, empty0 + 8u * stage, phase ^ 1u, 0x100u + stage)) { ok = false; break; }
+          tr_empty += diag_clock(tr) - c0;
           const uint32_t a_dst = smem_base + stage * stage_sz;
           const uint32_t b_dst = a_dst + kBlockM * kBlockK * 2;
-          const int nb0 = ti.n0 + crank * b_rows;   // first B row (C column) this CTA loads
-          if (p.debug_flags & 64) {
+          const uint32_t full = full0 + 8u * stage;
+          if (kDiag && no_loads) {
             // diagnostics: no operand loads, the MMAs run on whatever the stage holds
-            if (crank == 0) ptx::mbar_arrive(bar(BAR_FULL + stage));
+            if (crank == 0) ptx::mbar_arrive(full0_local + 8u * stage);
           } else if (CG == 1) {
-            ptx::mbar_expect_tx(bar(BAR_FULL + stage), stage_sz);
-            ptx::tma_load_2d(a_dst, tma_a, bar(BAR_FULL + stage), kb * kBlockK, ti.row0);
-            if (!p.b_mn_major) {
-              ptx::tma_load_2d(b_dst, tma_b, bar(BAR_FULL + stage), kb * kBlockK, nb0);
+            ptx::mbar_expect_tx(full, tx_bytes);
+            ptx::tma_load_2d(a_dst, tma_a, full, kx, row0);
+            if (!b_mn) {
+              ptx::tma_load_2d(b_dst, tma_b, full, kx, nb0);
             } else {
-              for (int c = 0; c < b_rows / 64; ++c)
-                ptx::tma_load_2d(b_dst + c * 8192, tma_b, bar(BAR_FULL + stage), nb0 + c * 64,
-                                 kb * kBlockK);
+              for (int c = 0; c < b_panels; ++c)
+                ptx::tma_load_2d(b_dst + c * 8192, tma_b, full, nb0 + c * 64, kx);
             }
           } else {
             // Both CTAs' bytes are counted on the leader's barrier; only the leader arrives.
-            const uint32_t full = lead(BAR_FULL + stage);
-            if (crank == 0) ptx::mbar_expect_tx(bar(BAR_FULL + stage), 2 * stage_sz);
-            ptx::tma_load_2d_pair(a_dst, tma_a, full, kb * kBlockK, ti.row0);
-            if (!p.b_mn_major) {
-              ptx::tma_load_2d_pair(b_dst, tma_b, full, kb * kBlockK, nb0);
+            if (crank == 0) ptx::mbar_expect_tx(full0_local + 8u * stage, tx_bytes);
+            ptx::tma_load_2d_pair(a_dst, tma_a, full, kx, row0);
+            if (!b_mn) {
+              ptx::tma_load_2d_pair(b_dst, tma_b, full, kx, nb0);
             } else {
-              for (int c = 0; c < b_rows / 64; ++c)
-                ptx::tma_load_2d_pair(b_dst + c * 8192, tma_b, full, nb0 + c * 64, kb * kBlockK);
+              for (int c = 0; c < b_panels; ++c)
+                ptx::tma_load_2d_pair(b_dst + c * 8192, tma_b, full, nb0 + c * 64, kx);
             }
           }
-          if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+          if (++stage == stages) { stage = 0; phase ^= 1u; }
         }
       }
       ok = __all_sync(0xffffffffu, ok);
     }
     if (OP == OP_AG && lane == 0) *s_progress = 0x7fffffffu;   // nothing left to pace against
+    if (tr && lane == 0) {
+      p.trace[blockIdx.x * 16 + 2] = tr_empty;
+      p.trace[blockIdx.x * 16 + 3] = tr_gather;
+    }
   } else if (warp == 1) {
-    // ---------------- MMA issuer (one thread) ----------------
+    // ---------------- MMA issuer (one warp, one elected lane issues) ----------------
+    // This loop feeds the tensor pipe and is bound by the latency of its own instruction stream:
+    // a k-block is four MMAs (512 tensor cycles at N = 256), and measured on B200 every cycle the
+    // issuing lane spends between two MMAs is a cycle the pipe idles (a loop that re-read
+    // parameters and built descriptors per MMA ran 765 cycles per k-block, this one 512-545).
+    // So: all loop state lives in registers (see the producer); the whole warp runs the loop
+    // with uniform control flow (wait results are combined with a vote), which lets the compiler
+    // keep that state in uniform registers; and each k-block's MMAs and commits are ONE statement
+    // that elects its issuing lane and advances the descriptors by adding to their low word.
     wc.where = (blockIdx.x << 8) | 1u;
-    if (lane == 0 && crank == 0) {
-      const uint32_t idesc = ptx::make_idesc_bf16(bn, p.b_mn_major, 128u * CG);
+    if (crank == 0) {
+      const int k_blocks = p.k_blocks, stages = p.stages;
+      const bool b_mn = p.b_mn_major != 0;
+      const uint32_t idesc = ptx::make_idesc_bf16(bn, b_mn ? 1u : 0u, 128u * CG);
+      const uint32_t desc_hi = static_cast<uint32_t>(ptx::make_smem_desc_sw128(0, 0, 1024) >> 32);
+      const uint32_t a_lo0 = static_cast<uint32_t>(ptx::make_smem_desc_sw128(smem_base, 16, 1024));
+      const uint32_t b_lo0 = static_cast<uint32_t>(
+          ptx::make_smem_desc_sw128(smem_base + kBlockM * kBlockK * 2, b_mn ? 8192 : 16, 1024));
+      const uint32_t b_kstep = b_mn ? (2048u >> 4) : (32u >> 4);
+      const uint32_t stage_step = static_cast<uint32_t>(stage_sz) >> 4;
+      const uint32_t full0 = bar(BAR_FULL);
+      const uint32_t empty_a = CG == 2 ? ptx::map_to_cta(bar(BAR_EMPTY), 0) : bar(BAR_EMPTY);
+      const uint32_t empty_b = CG == 2 ? ptx::map_to_cta(bar(BAR_EMPTY), 1) : 0u;
+      const uint32_t tfull_a = CG == 2 ? ptx::map_to_cta(bar(BAR_TFULL), 0) : bar(BAR_TFULL);
+      const uint32_t tfull_b = CG == 2 ? ptx::map_to_cta(bar(BAR_TFULL), 1) : 0u;
+      // the TMEM base was read from shared memory; a warp reduction makes it a uniform value
+      const uint32_t d_base = __reduce_or_sync(0xffffffffu, tmem_base);
+      const bool no_mma = diag(p, 128), no_full_wait = diag(p, 512 | 1024), no_release = diag(p, 1024);
       int stage = 0, acc = 0;
       uint32_t phase = 0, acc_phase = 0;
+      uint32_t a_lo = a_lo0, b_lo = b_lo0;
       bool ok = true;
-      for (int t = cta; t < total && ok; t += n_comp) {
-        if (!wait_mbar(wc, bar(BAR_TEMPTY + acc), acc_phase ^ 1u, 0x200u + acc)) break;
+      long long tr_tiles = 0;
+      const long long tr_begin = diag_clock(trc);
+      for (int t = cta; t < total; t += n_comp) {
+        if (!__all_sync(0xffffffffu,
+                        wait_mbar(wc, bar(BAR_TEMPTY + acc), acc_phase ^ 1u, 0x200u + acc)))
+          break;
+        ++tr_tiles;
         ptx::tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * 256;
-        for (int kb = 0; kb < p.k_blocks; ++kb) {
-          if (!wait_mbar(wc, bar(BAR_FULL + stage), phase, 0x300u + stage)) { ok = false; break; }
+        const uint32_t d_tmem = d_base + acc * 256;
+        uint32_t accumulate = 0u;
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!(kDiag && no_full_wait) &&
+              !__all_sync(0xffffffffu, wait_mbar(wc, full0 + 8u * stage, phase, 0x300u + stage))) {
+            ok = false;
+            break;
+          }
           ptx::tc_fence_after();
-          const uint32_t a_base = smem_base + stage * stage_sz;
-          const uint32_t b_base = a_base + kBlockM * kBlockK * 2;
-#pragma unroll
-          for (int k = 0; k < kBlockK / 16; ++k) {
-            if (p.debug_flags & 128) break;   // diagnostics: loads only, no MMAs
-            // A: K-major, 128-byte swizzle: rows are 128 B apart, 8-row groups 1024 B apart;
-            // a K step of 16 elements moves the start address by 32 B inside the swizzle row.
-            const uint64_t a_desc = ptx::make_smem_desc_sw128(a_base + k * 32, 16, 1024);
-            // B: same layout when stored [N,K]; when stored [K,N] the tile is held as 64-column
-            // panels (8192 B apart) of 64 k-rows x 128 B, and a K step of 16 moves by 2048 B.
-            const uint64_t b_desc =
-                p.b_mn_major ? ptx::make_smem_desc_sw128(b_base + k * 2048, 8192, 1024)
-                             : ptx::make_smem_desc_sw128(b_base + k * 32, 16, 1024);
-            if (CG == 1) ptx::umma_bf16(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0 ? 1u : 0u);
-            else ptx::umma_bf16_pair(d_tmem, a_desc, b_desc, idesc, (kb | k) != 0 ? 1u : 0u);
-          }
-          // stage reusable (in both CTAs of a pair) once these MMAs finish
-          if (CG == 1) {
-            ptx::umma_commit(bar(BAR_EMPTY + stage));
-          } else {
-            ptx::umma_commit_pair(ptx::map_to_cta(bar(BAR_EMPTY + stage), 0));
-            ptx::umma_commit_pair(ptx::map_to_cta(bar(BAR_EMPTY + stage), 1));
-          }
-          if (++stage == p.stages) { stage = 0; phase ^= 1u; }
+          if (kDiag && no_mma)
+            ptx::umma_commit_elect<CG>(empty_a + 8u * stage, empty_b + 8u * stage);
+          else
+            ptx::umma_kblock<CG>(d_tmem, a_lo, b_lo, b_kstep, desc_hi, idesc, accumulate,
+                                 empty_a + 8u * stage, empty_b + 8u * stage,
+                                 !(kDiag && no_release));
+          accumulate = 1u;
+          a_lo += stage_step;
+          b_lo += stage_step;
+          if (++stage == stages) { stage = 0; phase ^= 1u; a_lo = a_lo0; b_lo = b_lo0; }
         }
         if (!ok) break;
         // accumulator complete (each CTA of a pair holds its own 128 rows)
-        if (CG == 1) {
-          ptx::umma_commit(bar(BAR_TFULL + acc));
-        } else {
-          ptx::umma_commit_pair(ptx::map_to_cta(bar(BAR_TFULL + acc), 0));
-          ptx::umma_commit_pair(ptx::map_to_cta(bar(BAR_TFULL + acc), 1));
-        }
+        ptx::umma_commit_elect<CG>(tfull_a + 8u * acc, tfull_b + 8u * acc);
         acc ^= 1;
         if (acc == 0) acc_phase ^= 1u;
+      }
+      if (trc && lane == 0) {
+        unsigned long long* o = p.trace + blockIdx.x * 16;
+        o[6] = clock64() - tr_begin; o[9] = tr_tiles;
       }
     }
   } else if (warp == 2) {
@@ -326,9 +383,19 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
     uint32_t acc_phase = 0;
     const int sub_row = lane >> 3, piece = lane & 7;
     uint32_t entered_mask = 1u << s.rank;  // owners known to have entered this launch
+    long long tr_tfull = 0, tr_busy = 0;
+    // loop state in registers (see the producer)
+    const int N = s.N, world = s.world, rank = s.rank, part_rows = s.part_rows;
+    const long long ldc = p.ldc;
+    __nv_bfloat16* const c_local = static_cast<__nv_bfloat16*>(p.C);
+    __nv_bfloat16* const c_copy =
+        (OP == OP_AR && world == 1) ? static_cast<__nv_bfloat16*>(p.peer_out[0]) : nullptr;
+    const bool to_owner = OP == OP_RS && world > 1 && !diag(p, 2);
+    const uint32_t tfull0 = bar(BAR_TFULL), stored0 = bar(BAR_STORED);
+    const uint32_t tempty0 = CG == 2 ? lead(BAR_TEMPTY) : bar(BAR_TEMPTY);
     for (int t = cta; t < total; t += n_comp) {
       const TileInfo ti = tile_info(s, t);
-      if (OP == OP_RS && s.world > 1) {
+      if (OP == OP_RS && world > 1) {
         // Rows of this tile go into their owners' buffers: an owner's buffer may be written
         // only once that owner has entered this launch (its previous reduce has ended).
         int lo, hi;
@@ -343,16 +410,38 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
         }
         if (!__all_sync(0xffffffffu, ok)) break;
       }
-      if (!wait_mbar(wc, bar(BAR_TFULL + acc), acc_phase, 0x500u + acc)) break;
+      // Destination of the eight rows this lane stores per 64-column chunk (row it*4 + sub_row
+      // of the warp's 32): the local C, or for ReduceScatter the owner's buffer, in the slab
+      // reserved for this (producing) rank -- remote when owner != rank: posted NVLink writes.
+      __nv_bfloat16* row_ptr[8];
+#pragma unroll
+      for (int it = 0; it < 8; ++it) {
+        const int r_in_tile = quarter * 32 + it * 4 + sub_row;
+        const int grow = ti.row0 + r_in_tile;
+        if (r_in_tile >= ti.rows) {
+          row_ptr[it] = nullptr;
+        } else if (to_owner) {
+          int o = grow / part_rows;
+          if (o > world - 1) o = world - 1;
+          row_ptr[it] = static_cast<__nv_bfloat16*>(p.peer_data[o]) +
+                        static_cast<long long>(rank * part_rows + (grow - o * part_rows)) * ldc;
+        } else {
+          row_ptr[it] = c_local + static_cast<long long>(grow) * ldc;
+        }
+      }
+      const long long c0 = diag_clock(tr);
+      if (!wait_mbar(wc, tfull0 + 8u * acc, acc_phase, 0x500u + acc)) break;
+      const long long c1 = diag_clock(tr);
+      tr_tfull += c1 - c0;
       ptx::tc_fence_after();
       const uint32_t t_base = tmem_base + acc * 256 + (static_cast<uint32_t>(quarter * 32) << 16);
+      const uint32_t my_row = stage_buf + lane * 128;
       for (int c = 0; c < bn; c += 64) {
         const bool two = c + 32 < bn;
         uint32_t r0[32], r1[32];
         ptx::tmem_ld_32x32(t_base + c, r0);
         if (two) ptx::tmem_ld_32x32(t_base + c + 32, r1);
         ptx::tmem_ld_wait();
-        const uint32_t my_row = stage_buf + lane * 128;
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           uint4 v;
@@ -375,18 +464,15 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
         }
         __syncwarp();
         const int col = ti.n0 + c + piece * 8;
-        const bool col_ok = (piece < (two ? 8 : 4)) && (col + 8 <= s.N);
+        const bool col_ok = (piece < (two ? 8 : 4)) && (col + 8 <= N);
 #pragma unroll
         for (int it = 0; it < 8; ++it) {
           const int r = it * 4 + sub_row;            // row inside this warp's 32 rows
-          const int r_in_tile = quarter * 32 + r;
-          if (col_ok && r_in_tile < ti.rows) {
+          if (col_ok && row_ptr[it] != nullptr) {
             const uint4 v = ptx::ld_shared_v4(stage_buf + r * 128 + ((piece ^ (r & 7)) << 4));
-            const int grow = ti.row0 + r_in_tile;
-            ptx::st_global_v4(output_row<OP>(p, grow) + col, v);
-            if (OP == OP_AR && s.world == 1)   // one GPU: the partial product is the result
-              ptx::st_global_v4(static_cast<__nv_bfloat16*>(p.peer_out[0]) +
-                                    static_cast<long long>(grow) * p.ldc + col, v);
+            ptx::st_global_v4(row_ptr[it] + col, v);
+            if (OP == OP_AR && c_copy != nullptr)   // one GPU: the partial product is the result
+              ptx::st_global_v4(c_copy + (row_ptr[it] - c_local) + col, v);
           }
         }
         __syncwarp();
@@ -394,12 +480,17 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
       ptx::tc_fence_before();
       __syncwarp();
       if (lane == 0) {
-        if (CG == 1) ptx::mbar_arrive(bar(BAR_TEMPTY + acc));
-        else ptx::mbar_arrive_cluster(lead(BAR_TEMPTY + acc));
-        if (kSignals && s.world > 1) ptx::mbar_arrive(bar(BAR_STORED + acc));
+        if (CG == 1) ptx::mbar_arrive(tempty0 + 8u * acc);
+        else ptx::mbar_arrive_cluster(tempty0 + 8u * acc);
+        if (kSignals && world > 1) ptx::mbar_arrive(stored0 + 8u * acc);
       }
+      tr_busy += diag_clock(tr) - c1;
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
+    }
+    if (tr && warp == 4 && lane == 0) {
+      p.trace[blockIdx.x * 16 + 7] = tr_tfull;
+      p.trace[blockIdx.x * 16 + 8] = tr_busy;
     }
   }
 }
@@ -727,7 +818,7 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
           if (!__all_sync(0xffffffffu, ok)) return;
         }
       }
-      if (!(p.debug_flags & 1)) {
+      if (!diag(p, 1)) {
         if (bcast_ag && !nvls_ag) {
           char* fan[kMaxWorld - 1];
 #pragma unroll
@@ -735,12 +826,13 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
             fan[i] = i < W - 1 ? static_cast<char*>(p.peer_data[(s.rank - 1 - i + W) % W]) + base
                                : nullptr;
           push_span<R, kMaxWorld - 1>(local + base, fan, W - 1, n_vec, false, ring, lane,
-                                      p.debug_flags);
+                                      kDiag ? p.debug_flags : 0);
         } else if (p.push_bulk && !nvls_ag) {
           push_span_bulk<R>(local + base, dst + base, n_vec, ring, lane);
         } else {
           char* one[1] = {dst + base};
-          push_span<R, 1>(local + base, one, 1, n_vec, nvls_ag, ring, lane, p.debug_flags);
+          push_span<R, 1>(local + base, one, 1, n_vec, nvls_ag, ring, lane,
+                          kDiag ? p.debug_flags : 0);
         }
       }
       __syncwarp();
@@ -805,7 +897,7 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
       const long long v_begin = static_cast<long long>(c) * p.item_vecs;
       long long n_vec = piece_vecs - v_begin;
       if (n_vec > p.item_vecs) n_vec = p.item_vecs;
-      if (n_vec > 0 && !(p.debug_flags & 1)) {
+      if (n_vec > 0 && !diag(p, 1)) {
         const long long base = static_cast<long long>(row0) * row_bytes + v_begin * 16;
         if (nvls_ar) {
           reduce_span_nvls(static_cast<const char*>(p.mc_data) + base,
@@ -880,6 +972,10 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
   volatile uint32_t* s_progress = s_words + 3;  // AllGather: tile the TMA producer has reached
   volatile uint32_t* s_item = s_words + 8;   // [8,16): one queue slot per warp
   const bool is_comm = static_cast<int>(blockIdx.x) < p.n_comm;
+
+  const bool tr = kDiag && p.trace != nullptr;   // coarse counters
+  const long long tr_c0 = diag_clock(tr);
+  const uint64_t tr_t0 = tr ? global_timer_ns() : 0;
 
   WaitCtx wc;
   wc.status = p.status;
@@ -969,6 +1065,10 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
     ptx::tc_fence_after();
     if (CG == 1) ptx::tmem_dealloc(*s_tmem, 512);
     else ptx::tmem_dealloc_pair(*s_tmem, 512);
+  }
+  if (tr && threadIdx.x == 0) {
+    p.trace[blockIdx.x * 16 + 0] = clock64() - tr_c0;
+    p.trace[blockIdx.x * 16 + 1] = global_timer_ns() - tr_t0;
   }
   if (p.sync == nullptr || threadIdx.x != 0) return;
 

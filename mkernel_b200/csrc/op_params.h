@@ -36,6 +36,8 @@ struct OpParams {
   void* peer_out[kMaxWorld];
   void* mc_data;         // multicast alias of peer_data (or nullptr)
   void* mc_out;          // multicast alias of peer_out (or nullptr)
+  // Diagnostics build only: 16 counters per CTA (cycles each role spent waiting); else nullptr.
+  unsigned long long* trace;
 };
 
 }  // namespace mkb

@@ -37,7 +37,10 @@ struct Options {
   // (max error 0.0106 of the 1e-2 parity metric at 2 GPUs, against 0.0078 bounded for the fp32
   // sum in the reduce role), and the default path has to hold the parity tolerance.
   long long use_nvls = 0;
-  long long debug_flags = 0;
+  long long debug_flags = 0;  // timing diagnostics; only builds made with -DMKB_DIAG accept it
+  long long trace_ptr = 0;    // diagnostics build: device address of 16 counters per CTA
+  long long max_stages = 0;   // cap on the operand ring depth (0 = as many as fit)
+  long long l2_promo = 3;     // TMA descriptor L2 promotion: 0 none, 1 64 B, 2 128 B, 3 256 B
   // AllGather push pacing, in quarter raster groups (0 = unpaced).  Measured on B200: unpaced
   // pushes arrive long before they are consumed and slow the GEMM on both sides (W=8: 0.504 ms
   // unpaced, 0.445 at 4..8, 0.624 at 2 which starves the consumers; W=2: 0.418 / 0.404 / 0.396).
@@ -59,12 +62,33 @@ static long long* option_slot(const char* name) {
   if (!strcmp(name, "group_cols")) return &g_opt.group_cols;
   if (!strcmp(name, "use_nvls")) return &g_opt.use_nvls;
   if (!strcmp(name, "cta_pair")) return &g_opt.cta_pair;
+#ifdef MKB_DIAG
   if (!strcmp(name, "debug_flags")) return &g_opt.debug_flags;
+  if (!strcmp(name, "trace_ptr")) return &g_opt.trace_ptr;
+#endif
+  if (!strcmp(name, "max_stages")) return &g_opt.max_stages;
+  if (!strcmp(name, "l2_promo")) return &g_opt.l2_promo;
   if (!strcmp(name, "push_bulk")) return &g_opt.push_bulk;
   if (!strcmp(name, "ag_fanout")) return &g_opt.ag_fanout;
   if (!strcmp(name, "ag_lead")) return &g_opt.ag_lead;
   if (!strcmp(name, "ar_one_shot")) return &g_opt.ar_one_shot;
   return nullptr;
+}
+
+// Range check shared by mk_set_option and the environment parser.  Only n_comm accepts -1
+// (= heuristic); the device wait budget stays within [1 ms, 60 s] so that no configuration can
+// turn the bounded waits into unbounded ones.
+static const char* option_range_error(const char* name, long long v) {
+  if (!strcmp(name, "n_comm")) return v >= -1 && v <= 147 ? nullptr : "must be in [-1, 147]";
+  if (!strcmp(name, "wait_limit_ms")) return v >= 1 && v <= 60000 ? nullptr : "must be in [1, 60000]";
+  if (!strcmp(name, "block_n")) return v >= 0 && v <= 256 ? nullptr : "must be in [0, 256]";
+  if (!strcmp(name, "max_stages")) return v >= 0 && v <= kMaxStages ? nullptr : "must be in [0, 8]";
+  if (!strcmp(name, "l2_promo")) return v >= 0 && v <= 3 ? nullptr : "must be in [0, 3]";
+  if (!strcmp(name, "group_rows") || !strcmp(name, "group_cols") || !strcmp(name, "ag_lead"))
+    return v >= 0 && v <= 4096 ? nullptr : "must be in [0, 4096]";
+  if (!strcmp(name, "trace_ptr")) return nullptr;
+  if (!strcmp(name, "debug_flags")) return v >= 0 && v <= 0xffff ? nullptr : "must be in [0, 65535]";
+  return v >= 0 && v <= 1 ? nullptr : "must be 0 or 1";
 }
 
 // Start-up defaults from the environment, for callers that cannot reach mk_set_option (a launcher
@@ -83,10 +107,12 @@ struct EnvOptions {
       pos = end + 1;
       if (item.empty()) continue;
       const size_t eq = item.find('=');
-      long long* slot = eq == std::string::npos ? nullptr : option_slot(item.substr(0, eq).c_str());
+      const std::string name = eq == std::string::npos ? std::string() : item.substr(0, eq);
+      long long* slot = eq == std::string::npos ? nullptr : option_slot(name.c_str());
       char* tail = nullptr;
       const long long v = eq == std::string::npos ? 0 : strtoll(item.c_str() + eq + 1, &tail, 10);
-      if (!slot || !tail || *tail != 0 || tail == item.c_str() + eq + 1 || v < -1) {
+      if (!slot || !tail || *tail != 0 || tail == item.c_str() + eq + 1 ||
+          option_range_error(name.c_str(), v) != nullptr) {
         fprintf(stderr, "mkernel_b200: ignoring MKERNEL_B200_OPTIONS entry '%s'\n", item.c_str());
         continue;
       }
@@ -116,8 +142,13 @@ static int default_n_comm(int op, int world, int M, int N, int K, int num_sms) {
   return 0;
 }
 
-static int make_plan(int op, int rank, int world, int M, int N, int K, int b_layout, int num_sms,
-                     Plan* out) {
+static Options options_snapshot() {
+  std::lock_guard<std::mutex> g(g_opt_mu);
+  return g_opt;
+}
+
+static int make_plan(const Options& o, int op, int rank, int world, int M, int N, int K,
+                     int b_layout, int num_sms, Plan* out) {
   if (op < OP_GEMM || op > OP_AR) return set_error(MK_ERR_INVALID, "unknown op %d", op);
   if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world)
     return set_error(MK_ERR_INVALID, "rank/world out of range: rank=%d world=%d", rank, world);
@@ -131,11 +162,6 @@ static int make_plan(int op, int rank, int world, int M, int N, int K, int b_lay
     return set_error(MK_ERR_INVALID, "GEMM+ReduceScatter: M=%d not divisible by world=%d", M, world);
   if (num_sms <= 0) num_sms = 148;
 
-  Options o;
-  {
-    std::lock_guard<std::mutex> g(g_opt_mu);
-    o = g_opt;
-  }
   int n_comm = (int)o.n_comm >= 0 && world > 1 && op != OP_GEMM
                    ? (int)o.n_comm : default_n_comm(op, world, M, N, K, num_sms);
   if (n_comm > num_sms - 1) n_comm = num_sms - 1;
@@ -198,6 +224,7 @@ static int make_plan(int op, int rank, int world, int M, int N, int K, int b_lay
     pl.ring_slots = kRingInCtaDeep;
   pl.stages = num_stages_cg(bn, pl.cg, pl.ring_slots);
   pl.smem = smem_bytes_cg(bn, pl.cg, pl.ring_slots);
+  if (o.max_stages >= 2 && pl.stages > (int)o.max_stages) pl.stages = (int)o.max_stages;
   // a dedicated exchange CTA lays 8 warp rings over the stage region and what follows it
   if (pl.smem < 1024 + kSmemBarrierBytes + 8 * kRingDedicated * 32 * 16)
     return set_error(MK_ERR_INVALID, "internal: shared-memory plan too small for exchange rings");
@@ -221,9 +248,10 @@ struct MapKey {
   const void* base;
   uint64_t inner, outer, ld;
   uint32_t box_inner, box_outer;
+  int promo;
   bool operator==(const MapKey& o) const {
     return base == o.base && inner == o.inner && outer == o.outer && ld == o.ld &&
-           box_inner == o.box_inner && box_outer == o.box_outer;
+           box_inner == o.box_inner && box_outer == o.box_outer && promo == o.promo;
   }
 };
 struct MapCache {
@@ -235,9 +263,9 @@ struct MapCache {
 };
 
 static int encode_2d_bf16(CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer,
-                          uint64_t ld_elems, uint32_t box_inner, uint32_t box_outer) {
+                          uint64_t ld_elems, uint32_t box_inner, uint32_t box_outer, int promo) {
   static thread_local MapCache cache;
-  const MapKey k{base, inner, outer, ld_elems, box_inner, box_outer};
+  const MapKey k{base, inner, outer, ld_elems, box_inner, box_outer, promo};
   for (int i = 0; i < MapCache::kSlots; ++i) {
     if (cache.used[i] && cache.key[i] == k) { *map = cache.map[i]; return MK_OK; }
   }
@@ -256,7 +284,7 @@ static int encode_2d_bf16(CUtensorMap* map, const void* base, uint64_t inner, ui
   const cuuint32_t estr[2] = {1, 1};
   CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+                  static_cast<CUtensorMapL2promotion>(promo), CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS)
     return set_error(MK_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
   cache.key[cache.next] = k;
@@ -354,8 +382,9 @@ static int run_op(const OpArgs& a, cudaStream_t stream) {
   int sms = 0;
   int rc = device_sm_count(&sms);
   if (rc != MK_OK) return rc;
+  const Options o = options_snapshot();
   Plan pl;
-  rc = make_plan(a.op, a.rank, a.world, a.M, a.N, a.K, a.b_layout, sms, &pl);
+  rc = make_plan(o, a.op, a.rank, a.world, a.M, a.N, a.K, a.b_layout, sms, &pl);
   if (rc != MK_OK) return rc;
 
   OpParams p;
@@ -367,15 +396,12 @@ static int run_op(const OpArgs& a, cudaStream_t stream) {
   p.b_mn_major = pl.b_mn_major;
   p.n_comm = pl.n_comm;
   p.ring_slots = pl.ring_slots;
-  bool want_nvls = false;
-  {
-    std::lock_guard<std::mutex> g(g_opt_mu);
-    want_nvls = g_opt.use_nvls != 0;
-    p.debug_flags = (int)g_opt.debug_flags;
-    p.push_bulk = (int)g_opt.push_bulk;
-    p.ag_fanout = (int)g_opt.ag_fanout;
-    p.ag_lead_tiles = (int)(g_opt.ag_lead * pl.sched.group_rows * pl.sched.Q / 4);
-  }
+  const bool want_nvls = o.use_nvls != 0;
+  p.debug_flags = (int)o.debug_flags;
+  p.trace = reinterpret_cast<unsigned long long*>(static_cast<uintptr_t>(o.trace_ptr));
+  p.push_bulk = (int)o.push_bulk;
+  p.ag_fanout = (int)o.ag_fanout;
+  p.ag_lead_tiles = (int)(o.ag_lead * pl.sched.group_rows * pl.sched.Q / 4);
   if (a.world > 1 && a.op != OP_GEMM) {
     const int workers = (pl.grid - pl.n_comm) + 8 * pl.n_comm;
     if (a.op == OP_AG) {
@@ -388,11 +414,8 @@ static int run_op(const OpArgs& a, cudaStream_t stream) {
     }
   }
   p.epoch_arg = a.epoch;
-  {
-    std::lock_guard<std::mutex> g(g_opt_mu);
-    p.wait_limit_ns = (uint64_t)g_opt.wait_limit_ms * 1000000ull;
-    p.use_nvls = want_nvls ? 1 : 0;
-  }
+  p.wait_limit_ns = (uint64_t)o.wait_limit_ms * 1000000ull;
+  p.use_nvls = want_nvls ? 1 : 0;
   p.C = a.C;
   p.ldc = a.N;
   if (a.sync) {
@@ -423,13 +446,15 @@ static int run_op(const OpArgs& a, cudaStream_t stream) {
   }
 
   CUtensorMap ta, tb;
-  rc = encode_2d_bf16(&ta, a.A, (uint64_t)a.K, (uint64_t)a.a_rows, (uint64_t)a.K, kBlockK, kBlockM);
+  const int promo = (int)o.l2_promo;
+  rc = encode_2d_bf16(&ta, a.A, (uint64_t)a.K, (uint64_t)a.a_rows, (uint64_t)a.K, kBlockK, kBlockM,
+                      promo);
   if (rc != MK_OK) return rc;
   if (pl.b_mn_major)
-    rc = encode_2d_bf16(&tb, a.B, (uint64_t)a.N, (uint64_t)a.K, (uint64_t)a.N, 64, kBlockK);
+    rc = encode_2d_bf16(&tb, a.B, (uint64_t)a.N, (uint64_t)a.K, (uint64_t)a.N, 64, kBlockK, promo);
   else
     rc = encode_2d_bf16(&tb, a.B, (uint64_t)a.K, (uint64_t)a.N, (uint64_t)a.K, kBlockK,
-                        (uint32_t)(pl.sched.block_n / pl.cg));
+                        (uint32_t)(pl.sched.block_n / pl.cg), promo);
   if (rc != MK_OK) return rc;
   if ((reinterpret_cast<uintptr_t>(a.C) & 15) != 0)
     return set_error(MK_ERR_INVALID, "C must be 16-byte aligned");
@@ -476,8 +501,8 @@ int mk_set_option(const char* name, long long value) {
   std::lock_guard<std::mutex> g(g_opt_mu);
   long long* s = option_slot(name);
   if (!s) return set_error(MK_ERR_INVALID, "unknown option '%s'", name ? name : "(null)");
-  if (value < 0 && !(value == -1 && !strcmp(name, "n_comm")))
-    return set_error(MK_ERR_INVALID, "option '%s' must be >= 0", name);
+  if (const char* why = option_range_error(name, value))
+    return set_error(MK_ERR_INVALID, "option '%s' %s (got %lld)", name, why, value);
   *s = value;
   return MK_OK;
 }
@@ -604,7 +629,7 @@ int mk_gemm_rs_launch_noalloc(const void* A, const void* B, void* C, int M, int 
   int rc = device_sm_count(&sms);
   if (rc != MK_OK) return rc;
   Plan pl;
-  rc = make_plan(OP_RS, 0, 1, M, N, K, MK_B_NK, sms, &pl);
+  rc = make_plan(options_snapshot(), OP_RS, 0, 1, M, N, K, MK_B_NK, sms, &pl);
   if (rc != MK_OK) return rc;
   const long long need = sync_words_needed(pl.sched);
   if (need > kNoAllocSyncWords)
@@ -682,7 +707,7 @@ int mk_plan_op(int op, int rank, int world, int M, int N, int K, int b_layout, i
                mk_plan* out) {
   if (!out) return set_error(MK_ERR_INVALID, "mk_plan_op: null out");
   Plan pl;
-  int rc = make_plan(op, rank, world, M, N, K, b_layout, num_sms, &pl);
+  int rc = make_plan(options_snapshot(), op, rank, world, M, N, K, b_layout, num_sms, &pl);
   if (rc != MK_OK) return rc;
   out->block_n = pl.sched.block_n;
   out->stages = pl.stages;
@@ -720,7 +745,8 @@ int mk_sched_tiles(int op, int rank, int world, int M, int N, int block_n, int g
 
 int mk_sched_owner_items(int op, int world, int M, int N, int block_n, int owner, int* row0,
                          int* row1, int cap) {
-  if (world < 1 || world > kMaxWorld || owner < 0 || owner >= world || M < 1 || N < 1)
+  if (world < 1 || world > kMaxWorld || owner < 0 || owner >= world || M < 1 || N < 1 ||
+      block_n < 8)
     return set_error(MK_ERR_INVALID, "mk_sched_owner_items: bad arguments");
   const Sched s = make_sched(op, owner, world, M, N, block_n, 8);
   const int n = owner_num_items(s, owner);

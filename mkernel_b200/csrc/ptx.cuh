@@ -186,22 +186,6 @@ __device__ __forceinline__ void tc_fence_before() {
 __device__ __forceinline__ void tc_fence_after() {
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 }
-// D[tmem] (+)= A[smem desc] * B[smem desc]; bf16 inputs, fp32 accumulate; single-CTA form.
-__device__ __forceinline__ void umma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                          uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
-}
-// Arrive once on an mbarrier of this CTA when all previously issued MMAs have completed.
-__device__ __forceinline__ void umma_commit(uint32_t bar) {
-  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                   bar)
-               : "memory");
-}
 // 32 lanes x 32 consecutive fp32 columns: thread t of the warp receives lane (base+t).
 __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
@@ -264,23 +248,98 @@ __device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols
   asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
                : "memory");
 }
-// 256 x N x 16 MMA across a CTA pair: each CTA supplies its 128 rows of A and its half of B's N
-// columns from its own shared memory (same offsets in both), and receives its 128 rows of D.
-__device__ __forceinline__ void umma_bf16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc,
-                                               uint32_t idesc, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %4, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
-      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-      : "memory");
+// One k-block of MMAs as ONE statement, executed by a whole converged warp: four K=16 MMAs whose
+// shared-memory descriptors advance by a constant, then the commit(s) that hand the operand
+// stage back, all predicated on one elected lane inside the statement.  Written this way the
+// surrounding loop has no divergent branch, so the compiler can keep the loop state in uniform
+// registers, and the elected lane's instruction stream per k-block is as short as it gets (the
+// tensor pipe idles whenever that stream is late).
+// CG = 1: commit_b is ignored.  `accumulate` = 0 makes the first MMA overwrite the accumulator.
+template <int CG>
+__device__ __forceinline__ void umma_kblock(uint32_t d_tmem, uint32_t a_lo, uint32_t b_lo,
+                                            uint32_t b_kstep, uint32_t desc_hi, uint32_t idesc,
+                                            uint32_t accumulate, uint32_t commit_a,
+                                            uint32_t commit_b, bool do_commit) {
+  if (CG == 1) {
+    asm volatile(
+        "{\n\t.reg .pred pe, pa, pc;\n\t.reg .b64 da, db;\n\t.reg .b32 ra, rb;\n\t"
+        "elect.sync _|pe, 0xffffffff;\n\t"
+        "setp.ne.b32 pa, %6, 0;\n\t"
+        "setp.ne.and.b32 pc, %8, 0, pe;\n\t"
+        "mov.b64 da, {%1, %4};\n\t"
+        "mov.b64 db, {%2, %4};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pa;\n\t"
+        "setp.eq.b32 pa, 0, 0;\n\t"
+        "add.u32 ra, %1, 2;\n\t"
+        "add.u32 rb, %2, %3;\n\t"
+        "mov.b64 da, {ra, %4};\n\t"
+        "mov.b64 db, {rb, %4};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pa;\n\t"
+        "add.u32 ra, ra, 2;\n\t"
+        "add.u32 rb, rb, %3;\n\t"
+        "mov.b64 da, {ra, %4};\n\t"
+        "mov.b64 db, {rb, %4};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pa;\n\t"
+        "add.u32 ra, ra, 2;\n\t"
+        "add.u32 rb, rb, %3;\n\t"
+        "mov.b64 da, {ra, %4};\n\t"
+        "mov.b64 db, {rb, %4};\n\t"
+        "@pe tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, pa;\n\t"
+        "@pc tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%7];\n\t"
+        "}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(b_kstep), "r"(desc_hi), "r"(idesc),
+          "r"(accumulate), "r"(commit_a), "r"(do_commit ? 1u : 0u)
+        : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred pe, pa, pc;\n\t.reg .b64 da, db;\n\t.reg .b32 ra, rb;\n\t"
+        "elect.sync _|pe, 0xffffffff;\n\t"
+        "setp.ne.b32 pa, %6, 0;\n\t"
+        "setp.ne.and.b32 pc, %9, 0, pe;\n\t"
+        "mov.b64 da, {%1, %4};\n\t"
+        "mov.b64 db, {%2, %4};\n\t"
+        "@pe tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, pa;\n\t"
+        "setp.eq.b32 pa, 0, 0;\n\t"
+        "add.u32 ra, %1, 2;\n\t"
+        "add.u32 rb, %2, %3;\n\t"
+        "mov.b64 da, {ra, %4};\n\t"
+        "mov.b64 db, {rb, %4};\n\t"
+        "@pe tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, pa;\n\t"
+        "add.u32 ra, ra, 2;\n\t"
+        "add.u32 rb, rb, %3;\n\t"
+        "mov.b64 da, {ra, %4};\n\t"
+        "mov.b64 db, {rb, %4};\n\t"
+        "@pe tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, pa;\n\t"
+        "add.u32 ra, ra, 2;\n\t"
+        "add.u32 rb, rb, %3;\n\t"
+        "mov.b64 da, {ra, %4};\n\t"
+        "mov.b64 db, {rb, %4};\n\t"
+        "@pe tcgen05.mma.cta_group::2.kind::f16 [%0], da, db, %5, pa;\n\t"
+        "@pc tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%7];\n\t"
+        "@pc tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%8];\n\t"
+        "}\n"
+        ::"r"(d_tmem), "r"(a_lo), "r"(b_lo), "r"(b_kstep), "r"(desc_hi), "r"(idesc),
+          "r"(accumulate), "r"(commit_a), "r"(commit_b), "r"(do_commit ? 1u : 0u)
+        : "memory");
+  }
 }
-// Arrive once on an mbarrier (cluster address, either CTA) when all MMAs issued so far by this
-// thread for the pair have completed.
-__device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster_addr) {
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
-                   bar_cluster_addr)
-               : "memory");
+// The commit that publishes a finished accumulator, by the elected lane of a converged warp.
+template <int CG>
+__device__ __forceinline__ void umma_commit_elect(uint32_t bar_a, uint32_t bar_b) {
+  if (CG == 1) {
+    asm volatile(
+        "{\n\t.reg .pred pe;\n\t"
+        "elect.sync _|pe, 0xffffffff;\n\t"
+        "@pe tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}\n"
+        ::"r"(bar_a) : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred pe;\n\t"
+        "elect.sync _|pe, 0xffffffff;\n\t"
+        "@pe tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t"
+        "@pe tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%1];\n\t}\n"
+        ::"r"(bar_a), "r"(bar_b) : "memory");
+  }
 }
 
 // ---------------------------------------------------------------- descriptors

@@ -31,18 +31,18 @@ _EXPORTS = {
 }
 
 
-def load(name: str) -> types.ModuleType:
-    """Return the operator module ``mkernel_release_<name>``.
+def names() -> list[str]:
+    """Operator module names this library serves."""
+    return sorted(list(_EXPORTS) + list(multinode_compat.EXPORTS))
 
-    Raises RuntimeError if the name is not an operator of this library or the native library
-    has not been built (same failure mode as the reference when the .so is absent).
-    """
+
+def populate(mod: types.ModuleType, name: str) -> types.ModuleType:
+    """Fill `mod` with the attributes of operator module `name`.  Called by ``load`` and by the
+    import shims (csrc/loader_shim.c) that the reference's own loader imports as
+    ``build/lib<name>.so``."""
     if name not in _EXPORTS and name not in multinode_compat.EXPORTS:
-        raise RuntimeError(f"unknown kernel module '{name}'; available: "
-                           f"{sorted(list(_EXPORTS) + list(multinode_compat.EXPORTS))}")
+        raise RuntimeError(f"unknown kernel module '{name}'; available: {names()}")
     _lib.lib()  # fail loudly now if the native library is missing
-    mod_name = f"mkernel_release_{name}"
-    mod = types.ModuleType(mod_name, f"B200-native stand-in for build/lib{name}.so")
     mod.DistBuffer = DistBuffer
     if name in _EXPORTS:
         for attr in _EXPORTS[name]:
@@ -54,6 +54,20 @@ def load(name: str) -> types.ModuleType:
     if name == "gemm_rs_blackwell":
         mod.gemm_rs_blackwell_world_size = _lib.MK_MAX_WORLD
     mod.op_status = ops.op_status
+    mod.op_status_clear = ops.op_status_clear
+    mod.native_library = str(_lib.LIB_PATH)
+    return mod
+
+
+def load(name: str) -> types.ModuleType:
+    """Return the operator module ``mkernel_release_<name>``.
+
+    Raises RuntimeError if the name is not an operator of this library or the native library
+    has not been built (same failure mode as the reference when the .so is absent).
+    """
+    mod_name = f"mkernel_release_{name}"
+    mod = types.ModuleType(mod_name, f"B200-native stand-in for build/lib{name}.so")
+    populate(mod, name)
     mod.__file__ = str(_lib.LIB_PATH)
     sys.modules[mod_name] = mod
     return mod

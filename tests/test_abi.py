@@ -55,6 +55,37 @@ def test_options_roundtrip():
         _lib.set_option("block_n", -5)
     _lib.set_option("n_comm", 4)
     _lib.set_option("n_comm", -1)          # back to the heuristic
+    # only n_comm accepts -1; the device wait budget cannot be configured away
+    for name, bad in (("wait_limit_ms", -1), ("wait_limit_ms", 0), ("wait_limit_ms", 10 ** 9),
+                      ("ag_lead", -1), ("cta_pair", 2), ("block_n", 512), ("max_stages", 99)):
+        with pytest.raises(_lib.MkError):
+            _lib.set_option(name, bad)
+    assert _lib.get_option("wait_limit_ms") == 4000
+
+
+def test_environment_options_are_range_checked():
+    """MKERNEL_B200_OPTIONS goes through the same validation as mk_set_option: a bad entry is
+    reported and skipped, it never disables the bounded waits."""
+    import os
+    import subprocess
+    import sys
+    code = ("from mkernel_b200 import _lib; "
+            "print(_lib.get_option('wait_limit_ms'), _lib.get_option('block_n'), _lib.get_option('ag_lead'))")
+    env = dict(os.environ, MKERNEL_B200_OPTIONS="wait_limit_ms=-1,block_n=128,ag_lead=-1,bogus=3")
+    out = subprocess.run([sys.executable, "-c", code], env=env, capture_output=True, text=True,
+                         cwd=str(HEADER.parent.parent), check=True)
+    assert out.stdout.split() == ["4000", "128", "6"]
+    assert out.stderr.count("ignoring MKERNEL_B200_OPTIONS entry") == 3
+
+
+def test_debug_flags_exist_only_in_the_diagnostics_build():
+    with pytest.raises(_lib.MkError):
+        _lib.set_option("debug_flags", 1)
+
+
+def test_sched_owner_items_rejects_zero_block_n():
+    lib = _lib.lib()
+    assert lib.mk_sched_owner_items(_lib.OP_RS, 2, 256, 256, 0, 0, None, None, 0) == -1
 
 
 def test_view_validation_without_gpu():
