@@ -33,7 +33,7 @@ sys.path.insert(0, str(ROOT))
 CFG2 = dict(M=8192, N=3584, K=8192)          # AllGather+GEMM (headline), N is per rank
 CFG3 = dict(M=8192, N=8192, K=3584)          # GEMM+ReduceScatter, K is per rank
 CFG4 = dict(M=128, N=8192, K=1024)           # GEMM+AllReduce decode shape, K is per rank
-NVLINK_GBS = 900.0                           # per direction per GPU (nominal, per BASELINE)
+NVLINK_GBS = 900.0                           # per direction per GPU (nominal NVLink 5)
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0)
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one fused launch at the headline shape on one
@@ -200,6 +200,109 @@ class _Null:
         return False
 
 
+# ------------------------------------------------------------------------------------------------
+# parity (outside every timed region): the operators' outputs against the CPU oracle on sampled
+# rows and against an fp32 product of the same bf16 operands over all rows
+# ------------------------------------------------------------------------------------------------
+PARITY_TOL = 1e-2
+
+
+def error_figures(out, ref, rounded_scale=None):
+    """Error figures of a bf16 output against an fp32 reference, both on the same device.
+    rel_plain  = max |out - ref| / max(|ref|, rms(ref));
+    rel        = the same with the denominator also floored by `rounded_scale` (the sum over
+                 ranks of |partial|: everything that travelled as bf16 on the way to a reduced
+                 output); equal to rel_plain when no scale is given;
+    three_tier = the reference's own acceptance (bench/common.py:312-367: max_abs <= 0.35 or
+                 max_rel <= 0.08 or mean_abs <= 1 % of mean |ref|)."""
+    o, e = out.float(), ref.float()
+    d = (o - e).abs()
+    rms = e.pow(2).mean().sqrt().clamp_min(1e-30)
+    den = e.abs().clamp_min(rms)
+    plain = float((d / den).max())
+    rel = plain if rounded_scale is None else float((d / torch.maximum(den, rounded_scale.abs())).max())
+    max_abs, mean_abs, ref_mean = float(d.max()), float(d.mean()), float(e.abs().mean())
+    max_rel = float((d / e.abs().clamp_min(1e-6)).max())
+    tier = max_abs <= 0.35 or max_rel <= 0.08 or mean_abs <= 0.01 * max(ref_mean, 1e-6)
+    return {"rel": rel, "rel_plain": plain, "three_tier_ok": bool(tier)}
+
+
+def merge_parity(dst, rec):
+    """MAX of the error figures / AND of the verdicts over ranks; adds the overall verdict."""
+    if dst.dist is not None:
+        keys = sorted(k for k, v in rec.items() if isinstance(v, float))
+        t = torch.tensor([rec[k] for k in keys], dtype=torch.float64, device=dst.device)
+        dst.dist.all_reduce(t, op=dst.dist.ReduceOp.MAX)
+        for k, v in zip(keys, t.tolist()):
+            rec[k] = v
+        flags = sorted(k for k, v in rec.items() if isinstance(v, bool))
+        t = torch.tensor([1.0 if rec[k] else 0.0 for k in flags], dtype=torch.float64, device=dst.device)
+        dst.dist.all_reduce(t, op=dst.dist.ReduceOp.MIN)
+        for k, v in zip(flags, t.tolist()):
+            rec[k] = bool(v)
+    rec["tolerance"] = PARITY_TOL
+    rec["ok"] = bool(rec["rel"] <= PARITY_TOL and rec["rel_oracle"] <= PARITY_TOL and
+                     rec["three_tier_ok"] and rec.get("gathered_exact", True))
+    return rec
+
+
+def sum_over_ranks(dst, t):
+    if dst.dist is not None:
+        dst.dist.all_reduce(t)
+    return t
+
+
+def sample_rows(n_rows, count, seed):
+    g = torch.Generator().manual_seed(seed)
+    return torch.randperm(n_rows, generator=g)[:min(count, n_rows)].sort().values
+
+
+class NvlinkCounters:
+    """Bytes this GPU sent / received over NVLink, read from NVML's per-device throughput
+    counters (read-only field values; KiB, summed over links)."""
+
+    TX, RX = 138, 139      # NVML_FI_DEV_NVLINK_THROUGHPUT_DATA_TX / _RX
+
+    def __init__(self, index):
+        self.h = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.read()
+        except Exception:
+            self.h = None
+
+    def read(self):
+        if self.h is None:
+            return None
+        vals = self.nv.nvmlDeviceGetFieldValues(self.h, [(self.TX, 0xFFFFFFFF), (self.RX, 0xFFFFFFFF)])
+        out = []
+        for v in vals:
+            if v.nvmlReturn != 0:
+                raise RuntimeError("NVLink throughput counter not available")
+            out.append(int(v.value.ullVal) * 1024)
+        return out
+
+    def per_launch(self, fn, launches, sync):
+        """Runs fn `launches` times and returns {tx_bytes, rx_bytes} per launch, or None."""
+        if self.h is None:
+            return None
+        try:
+            sync()
+            a = self.read()
+            for i in range(launches):
+                fn(i)
+            sync()
+            time.sleep(0.05)
+            b = self.read()
+            return {"tx_bytes": (b[0] - a[0]) / launches, "rx_bytes": (b[1] - a[1]) / launches,
+                    "launches": launches}
+        except Exception as e:
+            return {"error": repr(e)[:120]}
+
+
 def randn_bf16(shape, seed, device, scale=1.0):
     g = torch.Generator(device=device).manual_seed(seed)
     return (torch.randn(shape, device=device, generator=g) * scale).to(torch.bfloat16)
@@ -211,11 +314,19 @@ def randn_bf16(shape, seed, device, scale=1.0):
 def run_ours(args):
     import mkernel_b200
     from mkernel_b200 import _lib, ops
+    from oracle import tp_gemm_oracle as orc      # the checker of the parity records only
 
     dst = Dist(args.gpus)
     W, rank, dev = dst.world, dst.local_rank, dst.device
     peaks, peak_kind = load_peaks()
     steps, warmup = args.steps, max(args.warmup, 3)
+    torch.backends.cuda.matmul.allow_tf32 = False          # fp32 checker products stay fp32
+    torch.set_float32_matmul_precision("highest")
+    cores = os.cpu_count() or 1
+    nvl = NvlinkCounters(rank) if W > 1 else None
+
+    def sync():
+        dst.barrier()
 
     # ---------------- headline: AllGather + GEMM ----------------
     M, N, K = CFG2["M"], CFG2["N"], CFG2["K"]
@@ -246,27 +357,99 @@ def run_ours(args):
     achieved = flops_per_gpu / (kern_ms * 1e-3) / 1e12
     ag_bytes = (W - 1) / W * M * K * 2
     t_roof_ms = max(flops_per_gpu / (peaks["bf16_tflops"] * 1e12), ag_bytes / (NVLINK_GBS * 1e9)) * 1e3
+    null_ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+    ag_nvlink = nvl.per_launch(lambda i: ag_step(i, *null_ev), 50, sync) if nvl else None
+
+    # sustained: the same launch back to back for at least a second (power-capped clocks)
+    sus_sampler = ClockSampler(rank)
+    sus_steps = max(200, int(1.2 / (kern_ms * 1e-3)))
+    sus_total, _ = timed_loop(dst, ag_step, sus_steps, 3, sus_sampler)
+    ag.op_status(ready)
+    sus_tflops = flops_per_gpu / (sus_total / sus_steps * 1e-3) / 1e12
+    sustained = {"seconds": sus_total * 1e-3, "launches": sus_steps, "tflops_per_gpu": sus_tflops,
+                 "peak": peaks["bf16_tflops_sustained"],
+                 "frac": sus_tflops / peaks["bf16_tflops_sustained"], "clocks": sus_sampler.summary()}
+
+    # ---------------- parity of the headline operator (untimed) ----------------
+    # Poison the remote slabs first so that a gather that did not happen would be noticed.
+    for r in range(W):
+        if r != rank:
+            A.data_[r].zero_()
+    C.zero_()
+    dst.barrier()
+    ag_step(0, *null_ev)
+    dst.barrier()
+    a_full = torch.cat([randn_bf16((Ms, K), 1 + r, dev) for r in range(W)], 0)
+    rec = {"gathered_exact": bool(torch.equal(A.data_.view(M, K), a_full))}
+    rec.update(error_figures(C.view(M, N), a_full.float() @ B.float().t()))
+    rows = sample_rows(M, 256, 11)
+    torch.set_num_threads(max(1, cores // W))
+    _, c_orc = orc.ag_gemm_ref([a_full[rows.to(dev)].cpu()], B.t().cpu())
+    rec["rel_oracle"] = orc.rel_error(C.view(M, N)[rows.to(dev)].cpu(), c_orc)
+    rec["rows_oracle"], rec["rows_fp32"] = int(rows.numel()), M
+    ag_parity = merge_parity(dst, rec)
+    del a_full
 
     # ---------------- end to end through the public API, host buffers ----------------
+    # Three streams: the host-to-device copy of step i+1, the kernel of step i and the
+    # device-to-host copy of step i-1 overlap; operands and outputs are double buffered.
     hA = randn_bf16((Ms, K), 1 + rank, "cpu").pin_memory()
     hB = B.cpu().pin_memory()
-    hC = torch.empty((W, Ms, N), dtype=torch.bfloat16).pin_memory()
-    dB = torch.empty_like(B)
+    A2 = ag.DistBuffer((W, Ms, K), dtype=torch.bfloat16, local_rank=rank, local_world_size=W)
+    ready2 = ag.DistBuffer((ag.ag_gemm_warp_specialized_ready_words,), dtype=torch.int32,
+                           local_rank=rank, local_world_size=W)
+    ready2.data_.zero_()
+    A2.data_.zero_()
+    bufA, bufR = (A, A2), (ready, ready2)
+    bufB = (torch.empty_like(B), torch.empty_like(B))
+    bufC = (C, torch.zeros_like(C))
+    hC = (torch.empty((W, Ms, N), dtype=torch.bfloat16).pin_memory(),
+          torch.empty((W, Ms, N), dtype=torch.bfloat16).pin_memory())
+    s_in, s_k, s_out = torch.cuda.Stream(), torch.cuda.Stream(), torch.cuda.Stream()
+    dst.barrier()
 
-    def e2e_step(i, e0, e1):
-        A.data_[rank].copy_(hA, non_blocking=True)
-        dB.copy_(hB, non_blocking=True)
-        ag.ag_gemm_warp_specialized_prepare(ready, M, N)
-        e0.record()
-        ag.ag_gemm_warp_specialized_launch(A, ready, dB, C)
-        e1.record()
-        hC.copy_(C, non_blocking=True)
+    def e2e_run(n):
+        ev_in = [torch.cuda.Event() for _ in range(n)]
+        ev_k = [torch.cuda.Event() for _ in range(n)]
+        ev_out = [torch.cuda.Event() for _ in range(n)]
+        for i in range(n):
+            b = i & 1
+            with torch.cuda.stream(s_in):
+                if i >= 2:
+                    s_in.wait_event(ev_k[i - 2])        # kernel i-2 has read these buffers
+                bufA[b].data_[rank].copy_(hA, non_blocking=True)
+                bufB[b].copy_(hB, non_blocking=True)
+                ev_in[i].record(s_in)
+            with torch.cuda.stream(s_k):
+                s_k.wait_event(ev_in[i])
+                if i >= 2:
+                    s_k.wait_event(ev_out[i - 2])       # output buffer has been read back
+                ag.ag_gemm_warp_specialized_prepare(bufR[b], M, N)
+                ag.ag_gemm_warp_specialized_launch(bufA[b], bufR[b], bufB[b], bufC[b])
+                ev_k[i].record(s_k)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(ev_k[i])
+                hC[b].copy_(bufC[b], non_blocking=True)
+                ev_out[i].record(s_out)
+        for st in (s_in, s_k, s_out):
+            torch.cuda.current_stream().wait_stream(st)
 
-    e2e_steps = max(3, min(steps, 10))
-    e2e_total, _ = timed_loop(dst, e2e_step, e2e_steps, 3)
+    e2e_steps = max(6, min(steps, 20))
+    e2e_run(4)
+    dst.barrier()
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0.record()
+    e2e_run(e2e_steps)
+    t1.record()
+    torch.cuda.synchronize()
+    dst.barrier()
+    e2e_total = dst.max_over_ranks(t0.elapsed_time(t1))
+    ag.op_status(ready)
+    ag.op_status(ready2)
+    e2e_ok = bool(torch.equal(hC[0], hC[1]) and torch.equal(hC[0].to(dev), C))
     e2e_value = W * flops_per_gpu / (e2e_total / e2e_steps * 1e-3) / 1e12
     h2d = hA.numel() * 2 + hB.numel() * 2
-    d2h = hC.numel() * 2
+    d2h = hC[0].numel() * 2
 
     # ---------------- unfused comparator for the headline ----------------
     ops_out = {}
@@ -287,7 +470,10 @@ def run_ours(args):
     _, ag_unf_ms = timed_loop(dst, ag_unfused, sub_steps, 3)
     ops_out["ag_gemm"] = op_record("AllGather+GEMM", CFG2, W, kern_ms, ag_unf_ms, flops_per_gpu,
                                    ag_bytes, peaks)
-    del A_full, C2, hA, hB, hC, dB
+    ops_out["ag_gemm"]["parity"] = ag_parity
+    ops_out["ag_gemm"]["nvlink_measured"] = ag_nvlink
+    del A_full, C2, hA, hB, hC, bufB, bufC
+    A2.free(); ready2.free()
 
     # ---------------- GEMM + ReduceScatter (config 3) ----------------
     M3, N3, K3 = CFG3["M"], CFG3["N"], CFG3["K"]
@@ -307,6 +493,7 @@ def run_ours(args):
 
     _, rs_ms = timed_loop(dst, rs_step, sub_steps, 3)
     rs.op_status(sync3)
+    rs_nvlink = nvl.per_launch(lambda i: rs_step(i, *null_ev), 50, sync) if nvl else None
     c3 = torch.empty((M3, N3), device=dev, dtype=torch.bfloat16)
     c3_rs = torch.empty((M3 // W, N3), device=dev, dtype=torch.bfloat16)
 
@@ -321,7 +508,32 @@ def run_ours(args):
     ops_out["gemm_rs"] = op_record("GEMM+ReduceScatter", CFG3, W, rs_ms, rs_unf_ms,
                                    2.0 * M3 * N3 * K3, (W - 1) / W * M3 * N3 * 2, peaks)
     del c3, c3_rs
+    # parity: this rank's rows of the sum over ranks of the fp32 partial products
+    dst.barrier()
+    rs_step(0, *null_ev)
+    dst.barrier()
+    Ms3 = M3 // W
+    part = A3.float() @ B3.float().t()
+    scale = sum_over_ranks(dst, part.abs())[rank * Ms3:(rank + 1) * Ms3].clone()
+    ref = sum_over_ranks(dst, part)[rank * Ms3:(rank + 1) * Ms3]
+    out3 = C3.data_[rank * Ms3:(rank + 1) * Ms3]
+    rec = error_figures(out3, ref, scale)
+    del part, ref, scale
+    per_owner = max(1, 256 // W)
+    grows = torch.cat([o * Ms3 + sample_rows(Ms3, per_owner, 12) for o in range(W)])
+    tot, parts = orc.gemm_ar_ref([A3[grows.to(dev)].cpu()], [B3.t().cpu()])
+    tot = sum_over_ranks(dst, tot.to(dev)).cpu()
+    sc = sum_over_ranks(dst, parts[0].abs().to(dev)).cpu()
+    mine = slice(rank * per_owner, (rank + 1) * per_owner)
+    own_rows = (grows[mine] - rank * Ms3).to(dev)
+    rec["rel_oracle"] = orc.rel_error(out3[own_rows].cpu(), tot[mine], sc[mine])
+    rec["rel_oracle_plain"] = orc.rel_error(out3[own_rows].cpu(), tot[mine])
+    rec["rows_oracle"], rec["rows_fp32"] = int(grows.numel()), M3
+    ops_out["gemm_rs"]["parity"] = merge_parity(dst, rec)
+    ops_out["gemm_rs"]["nvlink_measured"] = rs_nvlink
+    rs.op_status(sync3)
     C3.free(); sync3.free()
+    del A3, B3
 
     # ---------------- GEMM + AllReduce (config 4, decode shape) ----------------
     M4, N4, K4 = CFG4["M"], CFG4["N"], CFG4["K"]
@@ -342,6 +554,9 @@ def run_ours(args):
     ar_steps = max(20, sub_steps)
     _, ar_ms = timed_loop(dst, ar_step, ar_steps, 5)
     ar.op_status(bar4)
+    epoch_base = ar_steps + 5
+    ar_nvlink = nvl.per_launch(lambda i: ar_step(epoch_base + i, *null_ev), 200, sync) if nvl else None
+    epoch_base += 200
     c4 = torch.empty((M4, N4), device=dev, dtype=torch.bfloat16)
 
     def ar_unfused(i, e0, e1):
@@ -357,7 +572,31 @@ def run_ours(args):
     hbm_bytes = (M4 * K4 + K4 * N4 + 2 * M4 * N4) * 2
     rec["fused_us"] = ar_ms * 1e3
     rec["hbm_floor_us"] = hbm_bytes / (peaks["hbm_gbs"] * 1e9) * 1e6
-    rec["variant"] = "two-shot, peer loads/stores, per-tile flags, exit handshake"
+    rec["nvlink_measured"] = ar_nvlink
+    # parity: output identical on all ranks, partial and sum against fp32 and the oracle
+    C4f.data_.zero_()
+    dst.barrier()
+    ar_step(epoch_base, *null_ev)
+    epoch_base += 1
+    dst.barrier()
+    part = A4.float() @ B4.float()
+    par = error_figures(C4f.data_, sum_over_ranks(dst, part.clone()), sum_over_ranks(dst, part.abs()))
+    par["rel_partial"] = error_figures(C4.data_, part)["rel"]
+    tot, parts = orc.gemm_ar_ref([A4.cpu()], [B4.cpu()])
+    tot = sum_over_ranks(dst, tot.to(dev)).cpu()
+    sc = sum_over_ranks(dst, parts[0].abs().to(dev)).cpu()
+    par["rel_oracle"] = orc.rel_error(C4f.data_.cpu(), tot, sc)
+    par["rel_oracle_plain"] = orc.rel_error(C4f.data_.cpu(), tot)
+    par["rows_oracle"], par["rows_fp32"] = M4, M4
+    if W > 1:   # bit-identical output on every rank (bench/common.py:469-500)
+        bits = C4f.data_.view(torch.int16).to(torch.int32)
+        lo, hi = bits.clone(), bits.clone()
+        dst.dist.all_reduce(lo, op=dst.dist.ReduceOp.MIN)
+        dst.dist.all_reduce(hi, op=dst.dist.ReduceOp.MAX)
+        par["identical_across_ranks"] = bool(torch.equal(lo, hi))
+    rec["parity"] = merge_parity(dst, par)
+    if W > 1:
+        rec["parity"]["ok"] = rec["parity"]["ok"] and rec["parity"]["identical_across_ranks"]
     # The decode shape is latency-bound and an eager loop mostly measures host launch overhead,
     # so both arms are also timed as CUDA-graph replays of 10 launches (device-resident epoch).
     rec["graph_fused_us"], rec["graph_unfused_us"] = None, None
@@ -373,46 +612,67 @@ def run_ours(args):
         rec["graph_fused_us"] = graph_time_us(dst, fused_dev_epoch, 10, 10)
         rec["graph_unfused_us"] = graph_time_us(dst, unfused, 10, 10)
         ar.op_status(bar4)
+        # the replayed launches must still produce the checked result
+        rec["parity"]["graph_replay_rel"] = dst.max_over_ranks(error_figures(
+            C4f.data_, sum_over_ranks(dst, part.clone()), sum_over_ranks(dst, part.abs()))["rel"])
+        rec["parity"]["ok"] = rec["parity"]["ok"] and rec["parity"]["graph_replay_rel"] <= PARITY_TOL
     except Exception as e:  # graph capture of the comparator is best effort
         rec["graph_error"] = repr(e)[:200]
     ops_out["gemm_ar"] = rec
 
+    traffic = NCU_TRAFFIC_BYTES_PER_LAUNCH if W == 1 else None
     line = {
         "metric": "fused AG-GEMM TFLOPS (whole job; GEMM-RS / GEMM-AR under ops)",
         "value": value, "unit": "TFLOP/s", "per_gpu": value / W,
         "n_gpus": W, "steps": steps, "warmup": warmup, "ms_per_step": ms_per_step,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "AllGather+GEMM, Llama-70B MLP up-proj, TP=n_gpus: A shard "
-                               f"[{Ms},{K}] x B [{K},{N}] -> C [{M},{N}] per GPU",
-                   "M": M, "N_per_gpu": N, "K": K, "tp": W,
-                   "l2": "operands 246 MB per GPU exceed the 126 MB L2; no flush between steps",
-                   "step": "one fused persistent kernel (prepare is host-side validation only)"},
+        "config": headline_config(W),
         "roofline": {"bound": "tensor", "achieved": achieved, "peak": peaks["bf16_tflops"],
                      "unit": "TFLOP/s", "frac": achieved / peaks["bf16_tflops"],
-                     "frac_of_sustained": achieved / peaks["bf16_tflops_sustained"],
                      "peak_source": f"{peak_kind} (burst cuBLAS bf16)",
                      "kernel_ms": kern_ms, "fused_roofline_ms": t_roof_ms,
                      "fused_roofline_frac": t_roof_ms / kern_ms,
-                     "traffic": NCU_TRAFFIC_BYTES_PER_LAUNCH},
+                     "traffic": traffic,
+                     "traffic_note": ("DRAM bytes per launch from an ncu capture of the one-GPU case"
+                                      if W == 1 else
+                                      "not captured at this world size (a multi-rank launch is "
+                                      "never put under ncu); one-GPU figure: "
+                                      f"{NCU_TRAFFIC_BYTES_PER_LAUNCH:.3e} bytes"),
+                     "sustained": sustained},
         "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_total / e2e_steps},
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_total / e2e_steps,
+                "pipeline": "3 streams, double-buffered operands and outputs",
+                "outputs_match_device_result": e2e_ok},
         "gpu_launches": steps,
         "clocks": sampler.summary(),
+        "parity": {k: v["parity"]["ok"] for k, v in ops_out.items()},
         "ops": ops_out,
         "plan": plan_summary(_lib, W, rank),
     }
     if W == 1:
         line["cpu_baseline"] = cpu_baseline(CFG2, 1, budget_s=10.0)
+    all_ok = all(line["parity"].values()) and e2e_ok
     if dst.rank == 0:
         print(json.dumps(line), flush=True)
     dst.barrier()
     if dst.dist is not None:
         dst.dist.destroy_process_group()
+    if not all_ok:
+        raise SystemExit("parity check failed: see the 'parity' records of the line above")
+
+
+def headline_config(W):
+    M, N, K = CFG2["M"], CFG2["N"], CFG2["K"]
+    return {"workload": "AllGather+GEMM, Llama-70B MLP up-proj, TP=n_gpus: A shard "
+                        f"[{M // W},{K}] x B [{K},{N}] -> C [{M},{N}] per GPU",
+            "M": M, "N_per_gpu": N, "K": K, "tp": W,
+            "l2": "operands 246 MB per GPU exceed the 126 MB L2; no flush between steps",
+            "step": "one fused persistent kernel (prepare is host-side validation only)"}
 
 
 def run_sweep(args):
-    """BASELINE config 5: AllGather+GEMM and GEMM+ReduceScatter at total M in {2048, 8192, 32768},
+    """The scaling sweep: AllGather+GEMM and GEMM+ReduceScatter at total M in {2048, 8192, 32768},
     K = 8192, global N = 28672 sharded by the world size.  Prints one JSON line {"sweep": [...]}
     with TFLOP/s per GPU, the fused-roofline fraction and the unfused cuBLAS(+NCCL) time."""
     import mkernel_b200
@@ -662,8 +922,7 @@ def run_reference(args):
         "value": value, "unit": "TFLOP/s", "n_gpus": W, "steps": steps, "warmup": warmup,
         "ms_per_step": t_total / steps * 1e3, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "AllGather+GEMM, Llama-70B MLP up-proj, TP=n_gpus (bounded sample)",
-                   "M": cfg["M"], "N_per_gpu": cfg["N"], "K": cfg["K"], "tp": W},
+        "config": headline_config(W),
         "cpu_baseline": {"value": value, "unit": "TFLOP/s", "cores": torch.get_num_threads(),
                          "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -679,7 +938,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--sweep", action="store_true",
-                    help="time the M x world-size sweep (BASELINE config 5) instead of the headline")
+                    help="time the M x world-size sweep instead of the headline")
     ap.add_argument("--case", choices=["gemm", "ag", "rs", "ar"],
                     help="run one operator on one GPU a few times (a small case for a profiler)")
     ap.add_argument("--m", type=int, default=4096)

@@ -76,7 +76,13 @@ int mk_symm_get_view(const mk_symm* buf, mk_symm_view* out);
 /* ---- operators.  `stream` is a cudaStream_t.  All launches are asynchronous. ---------------- */
 
 /* Words (uint32) an operator's synchronisation buffer must hold.  The buffers are symmetric,
- * multicast not required, and must be zeroed once (see the *_prepare calls).
+ * multicast not required, and must be zeroed once before the first launch, on every rank, with
+ * all ranks synchronised afterwards: mk_gemm_rs_prepare does the zeroing; the AllGather `ready`
+ * and the AllReduce `barrier` buffers are zeroed by the caller (as in the reference's drivers).
+ * A buffer that was never zeroed gives each rank an arbitrary epoch and the first launch ends in
+ * a wait timeout.  After a device wait has expired (mk_op_status returns MK_ERR_DEVICE_WAIT)
+ * the status words stay set and every later launch on that buffer gives up at its first slow
+ * wait until mk_op_status_clear is called.
  * Reference: ag_gemm_warp_specialized_ready_words, gemm_rs_blackwell_sync_shape
  * (include/operators/ag_gemm/ag_gemm_warp_specialized_session.cuh:12-47,
  *  include/operators/gemm_rs/gemm_rs_blackwell_session.cuh:11-15), barrier (2,1024,1024). */
@@ -94,8 +100,11 @@ int mk_gemm_bf16(const void* A, const void* B, void* C, int M, int N, int K, int
  * (include/operators/ag_gemm/ag_gemm_warp_specialized.cuh:331-406,
  *  src/ag_gemm_warp_specialized.cu:115-134, 610-696).
  * A: symmetric [W, M/W, K] bf16, rank r has filled slab r.  ready: symmetric MK_AG_READY_WORDS.
- * B: [N, K] bf16.  C: [W, M/W, N] bf16 (M = total rows).  prepare is the all-rank entry barrier
- * and must precede every launch on the same stream. */
+ * B: [N, K] bf16.  C: [W, M/W, N] bf16 (M = total rows).  The reference's prepare is an all-rank
+ * entry barrier kernel; here the launch itself carries that ordering (every rank announces
+ * "entered launch e" to its peers and nobody writes into a peer's gathered buffer before seeing
+ * it), so prepare only validates `ready` and may be called or skipped; it does NOT zero
+ * `ready`. */
 int mk_ag_gemm_prepare(const mk_symm_view* ready, void* stream);
 int mk_ag_gemm_launch(const mk_symm_view* A, const mk_symm_view* ready, const void* B, void* C,
                       int M, int N, int K, void* stream);
@@ -128,8 +137,9 @@ int mk_gemm_rs_launch_ex(const void* A, const void* B, const mk_symm_view* C,
  * callers that cannot allocate device memory where they need the product (a process whose GPU
  * memory is fully owned by a pre-sized arena, or a path that must not hit cudaMalloc's device
  * synchronisation).  No counterpart in the reference.  Limits and rules:
- *  - world size 1 only; the output may have at most 16320 tiles of 128 x block_n
- *    (e.g. 8192 x 8192 is fine, 32768 x 28672 is rejected with MK_ERR_INVALID);
+ *  - world size 1 only; output tiles (128 x block_n) plus row-blocks (128 rows) may number at
+ *    most 16320 together (e.g. 8192 x 8192 is fine, 32768 x 28672 is rejected with
+ *    MK_ERR_INVALID);
  *  - the first call on each device looks up the array's device address; make that call
  *    before starting any stream capture;
  *  - all calls on a device share the one array: calls that overlap on the GPU (two streams)
@@ -167,9 +177,13 @@ int mk_op_status_clear(const mk_symm_view* sync, void* stream);
  *      receiver, 1 = an item loads its rows once and stores them to every peer), "push_bulk"
  *      (AllGather push through bulk shared-to-global stores), "ag_lead" (AllGather push pacing:
  *      rows are pushed at most this many quarter raster groups before the GEMM reaches the group
- *      that consumes them; default 6, 0 = push as fast as possible), "debug_flags" (timing diagnostics;
- *      results undefined).  The environment variable MKERNEL_B200_OPTIONS="name=value,..." sets
- *      start-up defaults when the library is loaded. */
+ *      that consumes them; default 6, 0 = push as fast as possible), "max_stages" (cap on the
+ *      operand ring depth, 0 = as many as fit), "l2_promo" (L2 promotion of the operand tensor
+ *      maps, 0..3 = none/64/128/256 bytes).  Values are range-checked (wait_limit_ms in
+ *      [1, 60000]; only n_comm accepts -1).  The environment variable
+ *      MKERNEL_B200_OPTIONS="name=value,..." sets start-up defaults when the library is loaded,
+ *      through the same checks.  Builds made with -DMKB_DIAG add "debug_flags" and "trace_ptr"
+ *      (timing diagnostics; results undefined); the default build rejects them. */
 int mk_set_option(const char* name, long long value);
 long long mk_get_option(const char* name);
 

@@ -136,6 +136,12 @@ __device__ __forceinline__ void stamp(const OpParams& p, int slot) {
     p.sync[24 + slot] = static_cast<uint32_t>(global_timer_ns());
 }
 
+// Same, keeping the latest time over all callers (the event's last occurrence in the launch).
+__device__ __forceinline__ void stamp_max(const OpParams& p, int slot) {
+  if (diag(p, 4) && p.sync != nullptr)
+    atomicMax(p.sync + 24 + slot, static_cast<uint32_t>(global_timer_ns()));
+}
+
 struct TileInfo {
   int rowblock, q, row0, rows, n0;
 };
@@ -358,13 +364,16 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
         const TileInfo ti = tile_info(s, t);
         if (!wait_mbar(wc, bar(BAR_STORED + acc), acc_phase, 0x400u + acc)) break;
         // The tile's rows have been stored (possibly to other GPUs); make them visible
-        // system-wide, then tell every owner whose rows intersect the tile.
-        ptx::fence_acq_rel_sys();
-        int lo, hi;
-        rowblock_owners(s, ti.rowblock, &lo, &hi);
-        const long long idx = SW_FLAGS + tile_flag_index(s, s.rank, ti.rowblock, ti.q);
-        for (int o = lo; o <= hi; ++o) ptx::st_relaxed_sys(p.peer_sync[o] + idx, epoch);
-        if (t == 0) stamp(p, 1);
+        // system-wide, then tell every owner whose rows intersect the tile.  (Not needed when
+        // the rows went into slabs that carry the epoch next to every data word.)
+        if (!(OP == OP_AR && s.ar_push == 2)) {
+          ptx::fence_acq_rel_sys();
+          int lo, hi;
+          rowblock_owners(s, ti.rowblock, &lo, &hi);
+          const long long idx = SW_FLAGS + tile_flag_index(s, s.rank, ti.rowblock, ti.q);
+          for (int o = lo; o <= hi; ++o) ptx::st_relaxed_sys(p.peer_sync[o] + idx, epoch);
+        }
+        stamp_max(p, 1);
         if (CG == 1) ptx::mbar_arrive(bar(BAR_TEMPTY + acc));
         else ptx::mbar_arrive_cluster(lead(BAR_TEMPTY + acc));
         acc ^= 1;
@@ -391,6 +400,10 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
     __nv_bfloat16* const c_copy =
         (OP == OP_AR && world == 1) ? static_cast<__nv_bfloat16*>(p.peer_out[0]) : nullptr;
     const bool to_owner = OP == OP_RS && world > 1 && !diag(p, 2);
+    const int slab_mode = OP == OP_AR ? s.ar_push : 0;    // second copy into the owner's slab
+    const bool to_slab = slab_mode != 0;
+    // bytes per slab row: plain bf16, or (mode 2) every 32-bit word followed by the epoch
+    const long long slab_pitch = static_cast<long long>(N) * (slab_mode == 2 ? 4 : 2);
     const uint32_t tfull0 = bar(BAR_TFULL), stored0 = bar(BAR_STORED);
     const uint32_t tempty0 = CG == 2 ? lead(BAR_TEMPTY) : bar(BAR_TEMPTY);
     for (int t = cta; t < total; t += n_comp) {
@@ -414,10 +427,20 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
       // of the warp's 32): the local C, or for ReduceScatter the owner's buffer, in the slab
       // reserved for this (producing) rank -- remote when owner != rank: posted NVLink writes.
       __nv_bfloat16* row_ptr[8];
+      char* slab_ptr[OP == OP_AR ? 8 : 1];
 #pragma unroll
       for (int it = 0; it < 8; ++it) {
         const int r_in_tile = quarter * 32 + it * 4 + sub_row;
         const int grow = ti.row0 + r_in_tile;
+        if (OP == OP_AR) {
+          slab_ptr[it] = nullptr;
+          if (to_slab && r_in_tile < ti.rows) {
+            int o = grow / part_rows;
+            if (o > world - 1) o = world - 1;
+            slab_ptr[it] = reinterpret_cast<char*>(p.peer_sync[o]) + kArSlabByteOffset +
+                           static_cast<long long>(rank * part_rows + (grow - o * part_rows)) * slab_pitch;
+          }
+        }
         if (r_in_tile >= ti.rows) {
           row_ptr[it] = nullptr;
         } else if (to_owner) {
@@ -473,6 +496,15 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
             ptx::st_global_v4(row_ptr[it] + col, v);
             if (OP == OP_AR && c_copy != nullptr)   // one GPU: the partial product is the result
               ptx::st_global_v4(c_copy + (row_ptr[it] - c_local) + col, v);
+            if (OP == OP_AR && slab_ptr[it] != nullptr) {
+              if (slab_mode == 2) {
+                // data word, epoch, data word, epoch: the reader needs no separate flag
+                ptx::st_global_v4(slab_ptr[it] + col * 4, make_uint4(v.x, epoch, v.y, epoch));
+                ptx::st_global_v4(slab_ptr[it] + col * 4 + 16, make_uint4(v.z, epoch, v.w, epoch));
+              } else {
+                ptx::st_global_v4(slab_ptr[it] + col * 2, v);
+              }
+            }
           }
         }
         __syncwarp();
@@ -485,9 +517,14 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
         if (kSignals && world > 1) ptx::mbar_arrive(stored0 + 8u * acc);
       }
       tr_busy += diag_clock(tr) - c1;
+      if (kDiag && t == cta && blockIdx.x == 0 && warp == 4 && lane == 0) stamp(p, 7);
       acc ^= 1;
       if (acc == 0) acc_phase ^= 1u;
     }
+    // Latency-bound AllReduce: the exchange warp holds back until this CTA's tiles are stored
+    // (its polling would compete with the operand stream for L2 bandwidth, and all ranks run the
+    // same GEMM, so the peers' rows cannot be there much earlier anyway).
+    if (OP == OP_AR && warp == 4 && lane == 0) *s_progress = 1u;
     if (tr && warp == 4 && lane == 0) {
       p.trace[blockIdx.x * 16 + 7] = tr_tfull;
       p.trace[blockIdx.x * 16 + 8] = tr_busy;
@@ -745,11 +782,101 @@ __device__ __forceinline__ void reduce_span_nvls(const char* mc_src, char* mc_ds
   }
 }
 
+// AllReduce from slabs whose every 32-bit data word is followed by the epoch of the launch that
+// wrote it (the producers' epilogues store them with 16-byte stores, so a data word and its
+// epoch always arrive together): the reader needs no flag, no fence and no second round trip --
+// it loads, and re-loads the vectors whose epoch words are not yet this launch's.  One output
+// vector (8 bf16) = two slab vectors per source rank.  fp32 sum in rank order, deterministic.
+template <int WT, int U>
+__device__ __noinline__ bool reduce_span_ll(const char* const (&src)[kMaxWorld],
+                                            char* const (&dst)[kMaxWorld], int W, int n_vec,
+                                            uint32_t epoch, int lane, const WaitCtx& wc) {
+  for (int v0 = lane; v0 < n_vec; v0 += 32 * U) {
+    uint4 a[U][WT][2];
+    // Load the whole batch, look at all epoch words, and re-load the whole batch while any of
+    // them is not this launch's: the loads of a batch stay independent of one another, so a
+    // retry costs one memory latency, not one per vector.
+    uint32_t it = 0;
+    uint64_t t0 = 0;
+    while (true) {
+      bool all = true;
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const long long off = static_cast<long long>(v0 + u * 32) * 32;
+        if (v0 + u * 32 < n_vec) {
+#pragma unroll
+          for (int c = 0; c < WT; ++c) {
+            if (c < W) {
+              a[u][c][0] = ptx::ld_relaxed_sys_v4(reinterpret_cast<const uint32_t*>(src[c] + off));
+              a[u][c][1] = ptx::ld_relaxed_sys_v4(reinterpret_cast<const uint32_t*>(src[c] + off + 16));
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (v0 + u * 32 < n_vec) {
+#pragma unroll
+          for (int c = 0; c < WT; ++c) {
+            if (c < W) {
+#pragma unroll
+              for (int h = 0; h < 2; ++h)
+                all = all && a[u][c][h].y == epoch && a[u][c][h].w == epoch;
+            }
+          }
+        }
+      }
+      if (all) break;
+      // bounded: same budget and abort protocol as every other wait of the kernel
+      ++it;
+      if (it > 8) __nanosleep(it > 1024 ? 400 : 60);
+      if ((it & 63u) == 0u) {
+        bool give_up = *wc.s_abort != 0u ||
+                       (wc.status != nullptr && ptx::ld_relaxed_sys(wc.status) != 0u);
+        const uint64_t now = global_timer_ns();
+        if (t0 == 0) t0 = now;
+        else if (!give_up && now - t0 > wc.limit_ns) {
+          report_failure(wc, ST_TIMEOUT_TILE, 0xFFu, static_cast<uint32_t>(v0));
+          give_up = true;
+        }
+        if (give_up) { *wc.s_abort = 1u; return false; }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int v = v0 + u * 32;
+      if (v >= n_vec) continue;
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int c = 0; c < WT; ++c) {
+        if (c >= W) continue;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const uint4 x = a[u][c][h];
+          acc[h * 4 + 0] += __uint_as_float(x.x << 16);
+          acc[h * 4 + 1] += __uint_as_float(x.x & 0xffff0000u);
+          acc[h * 4 + 2] += __uint_as_float(x.z << 16);
+          acc[h * 4 + 3] += __uint_as_float(x.z & 0xffff0000u);
+        }
+      }
+      uint4 r;
+      r.x = ptx::pack_bf16x2(acc[0], acc[1]);
+      r.y = ptx::pack_bf16x2(acc[2], acc[3]);
+      r.z = ptx::pack_bf16x2(acc[4], acc[5]);
+      r.w = ptx::pack_bf16x2(acc[6], acc[7]);
+#pragma unroll
+      for (int d = 0; d < WT; ++d)
+        if (d < W && dst[d] != nullptr) ptx::st_global_v4(dst[d] + static_cast<long long>(v) * 16, r);
+    }
+  }
+  return true;
+}
+
 // One exchange worker (a full warp).  Pulls items until the queue is empty.  Returns when done
-// or when a wait expired.  `s_item` is a shared-memory word private to this warp.
+// or when a wait expired.  `s_items_done` is the CTA's count of finished AllReduce items.
 template <int OP, int R>
 __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring, WaitCtx& wc,
-                                                uint32_t epoch, volatile uint32_t* s_item,
+                                                uint32_t epoch, volatile uint32_t* s_items_done,
                                                 volatile uint32_t* s_progress) {
   const Sched& s = p.sched;
   const int lane = threadIdx.x & 31;
@@ -764,16 +891,23 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
   const long long row_bytes = (OP == OP_AG ? static_cast<long long>(p.K) : static_cast<long long>(s.N)) * 2;
   char* const local = static_cast<char*>(p.peer_data[s.rank]);
   uint32_t entered_mask = 1u << s.rank;  // ranks known to have entered this launch
+  // Items normally come from a queue (an atomic counter), so that early items meet early data.
+  // The latency-bound AllReduce over epoch-carrying slabs hands them out statically instead --
+  // worker w takes items w, w + workers, ... -- which saves every worker the counter's round
+  // trip to L2 before its first load (every warp of the grid is a worker there).
+  const bool fixed_items = OP == OP_AR && s.ar_push == 2;
+  const uint32_t n_workers = gridDim.x * (kThreads / 32);
   uint32_t next_item = 0;
-  if (lane == 0) next_item = atomicAdd(p.sync + SW_NEXT_ITEM, 1u);
-  (void)s_item;
+  if (fixed_items) next_item = blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+  else if (lane == 0) next_item = atomicAdd(p.sync + SW_NEXT_ITEM, 1u);
 
   while (true) {
     // The queue is read one item ahead: the atomic for the next item is in flight while this
     // one is processed, so its round trip to L2 is off the critical path.
     const int item = static_cast<int>(__shfl_sync(0xffffffffu, next_item, 0));
     if (item >= p.n_items) break;
-    if (lane == 0) next_item = atomicAdd(p.sync + SW_NEXT_ITEM, 1u);
+    if (fixed_items) next_item += n_workers;
+    else if (lane == 0) next_item = atomicAdd(p.sync + SW_NEXT_ITEM, 1u);
 
     if (OP == OP_AG) {
       // Item order: row-block j of the own shard goes to every receiver (nearest ring distance
@@ -850,9 +984,10 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
       const int cpb = reduce_chunks_per_piece(s, p.item_vecs);
       const int k = item / cpb, c = item % cpb;
       const int rb = owner_first_block(s, s.rank) + k;
+      const bool ll = OP == OP_AR && s.ar_push == 2;   // slabs carry their own epochs: no flags
       // 1. the row-block is complete once every rank has published every column block of it
       uint32_t* summary = p.sync + SW_FLAGS + summary_flag_index(s, rb);
-      bool ready = ptx::ld_acquire_gpu(summary) == epoch;
+      bool ready = ll || ptx::ld_acquire_gpu(summary) == epoch;
       ready = __shfl_sync(0xffffffffu, ready, 0);
       if (!ready && c != 0) {
         // Only the worker holding the first chunk of a piece polls the W x Q tile flags (items
@@ -902,6 +1037,23 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
         if (nvls_ar) {
           reduce_span_nvls(static_cast<const char*>(p.mc_data) + base,
                            static_cast<char*>(p.mc_out) + base, n_vec, lane);
+        } else if (ll) {
+          const char* src[kMaxWorld];
+          char* dst[kMaxWorld];
+#pragma unroll
+          for (int r = 0; r < kMaxWorld; ++r) {
+            src[r] = r >= W ? nullptr
+                            : reinterpret_cast<const char*>(p.sync) + kArSlabByteOffset +
+                                  ((static_cast<long long>(r) * s.part_rows + (row0 - s.rank * s.part_rows)) *
+                                       row_bytes + v_begin * 16) * 2;
+            dst[r] = r >= W ? nullptr : static_cast<char*>(p.peer_out[r]) + base;
+          }
+          bool ok;
+          if (W <= 2) ok = reduce_span_ll<2, 4>(src, dst, W, static_cast<int>(n_vec), epoch, lane, wc);
+          else if (W <= 4) ok = reduce_span_ll<4, 2>(src, dst, W, static_cast<int>(n_vec), epoch, lane, wc);
+          else ok = reduce_span_ll<8, 1>(src, dst, W, static_cast<int>(n_vec), epoch, lane, wc);
+          if (!__all_sync(0xffffffffu, ok)) return;
+          if (item == 0 && lane == 0) stamp(p, 2);
         } else {
           ReduceSpan sp;
           sp.n_vec = static_cast<int>(n_vec);
@@ -910,9 +1062,14 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
 #pragma unroll
           for (int r = 0; r < kMaxWorld; ++r) {
             // RS: slab r of this rank's buffer holds rank r's partial of this rank's rows.
+            // AR with staging slabs: slab r of this rank's barrier buffer, same rows.
             sp.src[r] = r >= W ? nullptr
                         : (OP == OP_RS)
                             ? local + base + (static_cast<long long>(r) - s.rank) * s.part_rows * row_bytes
+                        : (OP == OP_AR && s.ar_push)
+                            ? reinterpret_cast<const char*>(p.sync) + kArSlabByteOffset +
+                                  (static_cast<long long>(r) * s.part_rows + (row0 - s.rank * s.part_rows)) * row_bytes +
+                                  v_begin * 16
                             : static_cast<const char*>(p.peer_data[r]) + base;
             sp.dst[r] = r >= W ? nullptr
                         : (OP == OP_RS) ? local + base : static_cast<char*>(p.peer_out[r]) + base;
@@ -925,21 +1082,31 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
         }
       }
       __syncwarp();
-      // AllReduce: results went to other GPUs; order them before the "item done" count
-      if (OP == OP_AR && lane == 0) ptx::fence_acq_rel_sys();
     }
 
-    // 3. AllReduce: the worker that completes the rank's last item tells every rank that this
-    //    rank has written its share of their outputs and no longer reads their partials.
+    // 3. AllReduce: count the item.  Its results went to other GPUs with plain stores; they are
+    //    made visible, and the rank's completion is announced, once per CTA at teardown (a
+    //    system-scope fence per item would serialise the warps of an SM behind one another).
     if (OP == OP_AR && lane == 0) {
-      const uint32_t done = atomicAdd(p.sync + SW_ITEMS_DONE, 1u);
-      if (done == static_cast<uint32_t>(p.n_items - 1)) {
-        stamp(p, 3);
-        ptx::fence_acq_rel_sys();
-        for (int r = 0; r < W; ++r) ptx::st_relaxed_sys(p.peer_sync[r] + SW_EXIT + s.rank, epoch);
-      }
+      atomicAdd(const_cast<uint32_t*>(s_items_done), 1u);
+      stamp_max(p, 6);
     }
     __syncwarp();
+  }
+}
+
+// AllReduce, once per CTA after all of its warps have finished: publish the results of the items
+// this CTA reduced, add them to the rank's count, and when that completes the rank's items tell
+// every rank that this rank has written its share of their outputs and reads no more partials.
+__device__ __forceinline__ void announce_reduced_items(const OpParams& p, uint32_t n_done,
+                                                       uint32_t epoch) {
+  if (n_done == 0u) return;
+  ptx::fence_acq_rel_sys();
+  const uint32_t before = atomicAdd(p.sync + SW_ITEMS_DONE, n_done);
+  if (before + n_done == static_cast<uint32_t>(p.n_items)) {
+    stamp(p, 3);
+    for (int r = 0; r < p.sched.world; ++r)
+      ptx::st_relaxed_sys(p.peer_sync[r] + SW_EXIT + p.sched.rank, epoch);
   }
 }
 
@@ -970,7 +1137,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
   volatile uint32_t* s_abort = s_words + 1;  // CTA-wide abort flag
   volatile uint32_t* s_epoch = s_words + 2;
   volatile uint32_t* s_progress = s_words + 3;  // AllGather: tile the TMA producer has reached
-  volatile uint32_t* s_item = s_words + 8;   // [8,16): one queue slot per warp
+  volatile uint32_t* s_items_done = s_words + 4;  // AllReduce: items this CTA's warps reduced
   const bool is_comm = static_cast<int>(blockIdx.x) < p.n_comm;
 
   const bool tr = kDiag && p.trace != nullptr;   // coarse counters
@@ -986,6 +1153,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
   if (threadIdx.x == 0) {
     *s_abort = 0u;
     *s_progress = 0u;
+    *s_items_done = 0u;
     uint32_t e = p.epoch_arg;
     // The epoch lives on the device (graph replays need no host state) unless the caller
     // supplies one (GEMM+AR and the multi-node style signatures pass a host epoch)
@@ -1036,17 +1204,29 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
   if (is_comm) {
     if (OP != OP_GEMM)
       exchange_worker<OP, kRingDedicated>(p, smem_base + warp * (kRingDedicated * 32 * 16), wc,
-                                          epoch, s_item + warp, nullptr);
+                                          epoch, s_items_done, nullptr);
   } else if (warp == 3) {
+    if (OP == OP_AR && s.ar_push == 2 && s.world > 1) {
+      wc.where = (blockIdx.x << 8) | 3u;
+      const bool ok = bounded_wait<true>(wc, [&] { return *s_progress != 0u; }, ST_TIMEOUT_PIPE,
+                                         0x600u, 0u);
+      (void)ok;   // on expiry the abort flag is up and the worker returns at its first wait
+    }
     if (OP != OP_GEMM) {
       if (p.ring_slots == kRingInCtaDeep)
-        exchange_worker<OP, kRingInCtaDeep>(p, xchg_ring, wc, epoch, s_item + warp, s_progress);
+        exchange_worker<OP, kRingInCtaDeep>(p, xchg_ring, wc, epoch, s_items_done, s_progress);
       else
-        exchange_worker<OP, kRingInCta>(p, xchg_ring, wc, epoch, s_item + warp, s_progress);
+        exchange_worker<OP, kRingInCta>(p, xchg_ring, wc, epoch, s_items_done, s_progress);
     }
   } else {
     compute_roles<OP, CG>(&tma_a, &tma_b, p, smem_base, bar_base, epi_stage, *s_tmem, wc, epoch,
                           s_progress);
+    // Latency-bound AllReduce over epoch-carrying slabs: its reduce items need no shared-memory
+    // ring, so every warp whose GEMM role has ended joins the exchange worker on the item queue.
+    if (OP == OP_AR && s.ar_push == 2 && s.world > 1) {
+      __syncwarp();
+      exchange_worker<OP, kRingInCta>(p, xchg_ring, wc, epoch, s_items_done, nullptr);
+    }
   }
 
   // ---------------- teardown ----------------
@@ -1071,6 +1251,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
     p.trace[blockIdx.x * 16 + 1] = global_timer_ns() - tr_t0;
   }
   if (p.sync == nullptr || threadIdx.x != 0) return;
+  if (OP == OP_AR && s.world > 1 && *s_abort == 0u) announce_reduced_items(p, *s_items_done, epoch);
 
   // ---------------- exit handshake (thread 0 of every CTA) ----------------
   wc.where = (blockIdx.x << 8) | 15u;

@@ -48,6 +48,12 @@ struct Options {
   long long ag_fanout = 0;   // AllGather push: load each row group once, store it to every peer
   long long push_bulk = 0;   // AllGather push through TMA bulk stores instead of LSU stores
   long long ar_one_shot = 0;  // GEMM+AR: 1 = every rank reduces all rows itself (no broadcast)
+  // GEMM+AR two-shot: the epilogue also stores partial rows into their owner's staging slabs
+  // (posted remote stores) and owners reduce from local memory, when the output fits the slabs.
+  // 2 = every 32-bit data word is stored together with the epoch, so owners need no flags and no
+  // fences (M x N <= 1 Mi elements, else as 1); 1 = plain slabs plus per-tile flags (M x N <=
+  // 2 Mi elements, else as 0); 0 = owners always fetch the partials from their producers.
+  long long ar_push = 2;
   long long cta_pair = 1;   // 1: run compute CTAs as pairs (two-SM MMA) when the shape allows
 };
 static Options g_opt;
@@ -72,6 +78,7 @@ static long long* option_slot(const char* name) {
   if (!strcmp(name, "ag_fanout")) return &g_opt.ag_fanout;
   if (!strcmp(name, "ag_lead")) return &g_opt.ag_lead;
   if (!strcmp(name, "ar_one_shot")) return &g_opt.ar_one_shot;
+  if (!strcmp(name, "ar_push")) return &g_opt.ar_push;
   return nullptr;
 }
 
@@ -88,6 +95,7 @@ static const char* option_range_error(const char* name, long long v) {
     return v >= 0 && v <= 4096 ? nullptr : "must be in [0, 4096]";
   if (!strcmp(name, "trace_ptr")) return nullptr;
   if (!strcmp(name, "debug_flags")) return v >= 0 && v <= 0xffff ? nullptr : "must be in [0, 65535]";
+  if (!strcmp(name, "ar_push")) return v >= 0 && v <= 2 ? nullptr : "must be 0, 1 or 2";
   return v >= 0 && v <= 1 ? nullptr : "must be 0 or 1";
 }
 
@@ -402,14 +410,24 @@ static int run_op(const OpArgs& a, cudaStream_t stream) {
   p.push_bulk = (int)o.push_bulk;
   p.ag_fanout = (int)o.ag_fanout;
   p.ag_lead_tiles = (int)(o.ag_lead * pl.sched.group_rows * pl.sched.Q / 4);
+  if (a.sync && a.op == OP_AR && o.ar_push != 0 && !want_nvls &&
+      sync_words_needed(pl.sched) * 4 <= kArSlabByteOffset) {
+    if (o.ar_push >= 2 && ar_push_fits(pl.sched, (long long)a.sync->bytes, 2)) pl.sched.ar_push = 2;
+    else if (ar_push_fits(pl.sched, (long long)a.sync->bytes, 1)) pl.sched.ar_push = 1;
+  }
+  p.sched = pl.sched;
   if (a.world > 1 && a.op != OP_GEMM) {
-    const int workers = (pl.grid - pl.n_comm) + 8 * pl.n_comm;
+    // Exchange workers: one warp per compute CTA (eight per dedicated exchange CTA).  With the
+    // epoch-carrying slabs of the latency-bound AllReduce every warp of a CTA turns into a worker
+    // once its GEMM role has finished, and a piece is cut accordingly finer.
+    const bool all_warps = a.op == OP_AR && pl.sched.ar_push == 2;
+    const int workers = (all_warps ? 8 : 1) * (pl.grid - pl.n_comm) + 8 * pl.n_comm;
     if (a.op == OP_AG) {
       p.item_vecs = 0;
       p.n_items = gather_num_items(pl.sched, p.ag_fanout != 0 ||
                                                  (want_nvls && a.data && a.data->mc != nullptr));
     } else {
-      p.item_vecs = choose_item_vecs(pl.sched, workers);
+      p.item_vecs = choose_item_vecs(pl.sched, workers, all_warps ? 32 : 128);
       p.n_items = reduce_num_items(pl.sched, a.rank, p.item_vecs);
     }
   }
@@ -602,7 +620,8 @@ int mk_gemm_rs_launch_ex(const void* A, const void* B, const mk_symm_view* C,
 // In host code the array's name is only a handle for the runtime, not a device address: the
 // address is looked up once per device with cudaGetSymbolAddress and that pointer is what the
 // kernel receives.
-constexpr int kNoAllocSyncWords = 16384;  // 64 KiB: header (64 words) + one word per output tile
+constexpr int kNoAllocSyncWords = 16384;  // 64 KiB: header (64 words) + one word per output
+                                          // tile + one per row-block
 static __device__ __align__(256) uint32_t g_noalloc_sync_words[kNoAllocSyncWords];
 
 static int noalloc_sync_address(uint32_t** out) {
@@ -635,7 +654,7 @@ int mk_gemm_rs_launch_noalloc(const void* A, const void* B, void* C, int M, int 
   if (need > kNoAllocSyncWords)
     return set_error(MK_ERR_INVALID,
                      "mk_gemm_rs_launch_noalloc: %d x %d output needs %lld synchronisation words, "
-                     "the built-in buffer holds %d (at most %d output tiles); use "
+                     "the built-in buffer holds %d (tiles plus row-blocks at most %d); use "
                      "mk_gemm_rs_launch with a caller-provided buffer",
                      M, N, need, kNoAllocSyncWords, kNoAllocSyncWords - SW_FLAGS);
   uint32_t* words = nullptr;

@@ -74,6 +74,9 @@ struct Sched {
   int group_cols;  // raster group width in column blocks (Q = the whole width)
   int interleave;  // RS/AR: 1 when part_rows % 128 == 0 (owner-interleaved order)
   int one_shot;    // AR only: every rank reduces every row for itself (no result broadcast)
+  int ar_push;     // AR only: partial rows are also stored into their owner's staging slabs (in
+                   // the upper half of the barrier buffer), so owners reduce from local memory.
+                   // 1: plain slabs + tile flags; 2: slabs whose data words carry the epoch
 };
 
 MKB_HD int ceil_div(int a, int b) { return (a + b - 1) / b; }
@@ -96,6 +99,7 @@ MKB_HD Sched make_sched(int op, int rank, int world, int M, int N, int block_n, 
   s.interleave = ((op == OP_RS || op == OP_AR) && world > 1 && (s.part_rows % kBlockM) == 0 &&
                   s.part_blocks * world == s.P) ? 1 : 0;
   s.one_shot = 0;
+  s.ar_push = 0;
   return s;
 }
 
@@ -187,6 +191,19 @@ MKB_HD void owner_item_rows(const Sched& s, int o, int k, int* row0, int* row1) 
   *row0 = a; *row1 = b;
 }
 
+// GEMM+AllReduce staging slabs: the reference's barrier buffer is 8 MiB (2 x 1024 x 1024 words)
+// and the flags of a latency-bound shape need a few KiB of it; the upper 4 MiB hold, on every
+// rank o, W slabs [part_rows][N] bf16: slab s = rank s's partial of o's rows.
+constexpr long long kArSlabByteOffset = 4ll << 20;
+constexpr long long kArSlabBytes = 4ll << 20;
+// `mode` 1: plain bf16 slabs plus per-tile flags; 2: every data word followed by the epoch (twice
+// the bytes, no flags).
+MKB_HD bool ar_push_fits(const Sched& s, long long sync_bytes, int mode) {
+  return s.op == OP_AR && s.world > 1 && !s.one_shot &&
+         sync_bytes >= kArSlabByteOffset + kArSlabBytes &&
+         (long long)s.world * s.part_rows * s.N * 2 * mode <= kArSlabBytes;
+}
+
 // Flag indices (relative to SW_FLAGS).
 MKB_HD long long tile_flag_index(const Sched& s, int src, int rb, int q) {
   return ((long long)src * s.P + rb) * s.Q + q;
@@ -217,7 +234,7 @@ MKB_HD int reduce_chunks_per_piece(const Sched& s, int item_vecs) {
 MKB_HD int reduce_num_items(const Sched& s, int owner, int item_vecs) {
   return owner_num_items(s, owner) * reduce_chunks_per_piece(s, item_vecs);
 }
-MKB_HD int choose_item_vecs(const Sched& s, int workers) {
+MKB_HD int choose_item_vecs(const Sched& s, int workers, int min_vecs = 128) {
   // A row-block's rows become reducible all at once (when its last tile lands on the last
   // rank), and the final row-block only at the very end of the GEMM: cut one piece (<= 128 rows)
   // into about one item per worker so that this tail is a single short round for everybody.
@@ -225,7 +242,7 @@ MKB_HD int choose_item_vecs(const Sched& s, int workers) {
   const int rows = (s.part_rows < kBlockM && !s.one_shot) ? s.part_rows : kBlockM;
   const long long piece = (long long)rows * s.N / 8;
   long long v = (piece + workers - 1) / workers;
-  if (v < 128) v = 128;
+  if (v < min_vecs) v = min_vecs;
   if (v > 4096) v = 4096;
   return (int)((v + 31) / 32 * 32);
 }

@@ -45,7 +45,7 @@ def bf16_round_np(x: np.ndarray) -> np.ndarray:
 
 def synth_inputs(kind: str, rank: int, world: int, M: int, N: int, K: int, seed: int,
                  sigma_b: float | None = None):
-    """Seeded synthetic operands with the distributions BASELINE's configs state:
+    """Seeded synthetic operands with the distributions of the benchmark configurations:
     A ~ N(0,1), B ~ N(0, sigma_b^2) with sigma_b = 1/sqrt(K_total) unless given; seed + rank.
 
     kind "ag": A_r [M/W, K], B [K, N] (logical).   kind "rs"/"ar": A_r [M, K], B_r [K, N]

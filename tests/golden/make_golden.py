@@ -1,7 +1,7 @@
 """Generates the fixtures in this directory.  Run once, in a container that has the reference
 tree mounted; the tests only read the generated files.
 
-    python tests/golden/make_golden.py /root/reference
+    python tests/golden/make_golden.py <path to a checkout of uccl-project/mKernel>
 
 1. check_close_cases.json -- verdicts of the REFERENCE's own acceptance function
    (bench/common.py:312-367, imported from the reference tree and run unmodified in a
@@ -10,7 +10,7 @@ tree mounted; the tests only read the generated files.
 2. torch_path_w2.npz -- outputs of the reference's torch path (torch.matmul +
    torch.distributed all_gather / reduce_scatter / all_reduce, bench/ag_gemm_bench.py:567-568,
    bench/gemm_rs_bench.py:408-410, bench/gemm_ar_blackwell_bench.py:423-425) run as two gloo
-   ranks on seeded bf16 inputs, plus BASELINE config 1 (fp32, 256x256 @ 256x512, all_reduce).
+   ranks on seeded bf16 inputs, plus the plumbing case (fp32, 256x256 @ 256x512, all_reduce).
    Outputs are stored subsampled (every 8th row and column) with their full-tensor sums.
 """
 from __future__ import annotations
@@ -105,7 +105,7 @@ def _torch_path_rank(rank: int, world: int, port: int, q):
     out["ar_partial"] = c.clone()
     dist.all_reduce(c, op=dist.ReduceOp.SUM)
     out["ar_out"] = c
-    # BASELINE config 1: fp32, A_r [256,256], B_r [256,512], A~N(0,1), B~N(0,1/256), seed 0 + r
+    # the plumbing case: fp32, A_r [256,256], B_r [256,512], A~N(0,1), B~N(0,1/256), seed 0 + r
     g = torch.Generator().manual_seed(0 + rank)
     a1 = torch.randn((256, 256), generator=g)
     b1 = torch.randn((256, 512), generator=g) * (1.0 / 16.0)
@@ -137,6 +137,7 @@ def gen_torch_path():
 
 
 if __name__ == "__main__":
-    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    ref_root = Path(sys.argv[1] if len(sys.argv) > 1 else
+                    Path(__file__).resolve().parents[3] / "reference")
     gen_torch_path()
     gen_check_close(ref_root)

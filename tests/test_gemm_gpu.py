@@ -68,7 +68,7 @@ def test_gemm_exact_on_small_integers():
 
 
 def test_gemm_linearity_at_headline_size():
-    """Size-independent property at the BASELINE config-2 GEMM shape (8192 x 3584 x 8192):
+    """Size-independent property at the up-projection GEMM shape (8192 x 3584 x 8192):
     scaling A by 2 scales every output by exactly 2 (a power of two commutes with rounding), and
     64 sampled rows agree with the oracle."""
     dev = torch.device("cuda:0")

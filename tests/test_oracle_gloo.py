@@ -1,6 +1,6 @@
 """The multi-rank semantics of the path on CPU ranks (gloo, world size 2): the reference's own
 torch path -- torch.matmul + all_gather / reduce_scatter / all_reduce -- must agree with the
-oracle's single-process restatement, including BASELINE config 1 (fp32, 256x256 @ 256x512,
+oracle's single-process restatement, including the plumbing case (fp32, 256x256 @ 256x512,
 all_reduce over 2 ranks)."""
 import os
 
@@ -18,7 +18,7 @@ def _rank(rank, world, port, q):
     dist.init_process_group("gloo", rank=rank, world_size=world)
     torch.set_num_threads(2)
     out = {}
-    # BASELINE config 1
+    # the plumbing case: fp32 operands, two ranks
     g = torch.Generator().manual_seed(0 + rank)
     a = torch.randn((256, 256), generator=g)
     b = torch.randn((256, 512), generator=g) / 16.0
@@ -50,7 +50,8 @@ def test_gloo_ranks_match_oracle():
     world = 2
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29800 + os.getpid() % 100
+    from tests.conftest import free_port
+    port = free_port()
     procs = [ctx.Process(target=_rank, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()

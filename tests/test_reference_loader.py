@@ -26,7 +26,8 @@ import pytest
 from mkernel_b200 import build as mkbuild
 from mkernel_b200 import load_module
 
-REFERENCE = Path(os.environ.get("MKERNEL_REFERENCE_DIR", "/root/reference"))
+REFERENCE = Path(os.environ.get("MKERNEL_REFERENCE_DIR") or
+                 Path(__file__).resolve().parents[2] / "reference")
 needs_reference = pytest.mark.skipif(not (REFERENCE / "python" / "load_module.py").exists(),
                                      reason="no checkout of the reference on this machine")
 

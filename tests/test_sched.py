@@ -6,7 +6,7 @@ from mkernel_b200 import _lib
 from mkernel_b200._lib import OP_AG, OP_AR, OP_GEMM, OP_RS
 
 CONFIGS = [
-    # op, world, M, N, K, layout   (BASELINE configs 2, 3, 4 and sweep corners)
+    # op, world, M, N, K, layout   (the three headline shapes and the corners of the M x world-size sweep)
     (OP_AG, 8, 8192, 3584, 8192, 0),
     (OP_RS, 8, 8192, 8192, 3584, 0),
     (OP_AR, 8, 128, 8192, 1024, 1),
