@@ -264,15 +264,15 @@ class NvlinkCounters:
     TX, RX = 138, 139      # NVML_FI_DEV_NVLINK_THROUGHPUT_DATA_TX / _RX
 
     def __init__(self, index):
-        self.h = None
+        self.h, self.why = None, None
         try:
             import pynvml
             pynvml.nvmlInit()
             self.nv = pynvml
             self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
             self.read()
-        except Exception:
-            self.h = None
+        except Exception as e:
+            self.h, self.why = None, repr(e)[:160]
 
     def read(self):
         if self.h is None:
@@ -281,14 +281,15 @@ class NvlinkCounters:
         out = []
         for v in vals:
             if v.nvmlReturn != 0:
-                raise RuntimeError("NVLink throughput counter not available")
+                raise RuntimeError(f"NVML NVLink throughput field returned error {v.nvmlReturn} "
+                                   "(3 = not supported on this system)")
             out.append(int(v.value.ullVal) * 1024)
         return out
 
     def per_launch(self, fn, launches, sync):
         """Runs fn `launches` times and returns {tx_bytes, rx_bytes} per launch, or None."""
         if self.h is None:
-            return None
+            return {"unavailable": self.why}
         try:
             sync()
             a = self.read()

@@ -116,6 +116,15 @@ int mk_ag_gemm_launch(const mk_symm_view* A, const mk_symm_view* ready, const vo
 int mk_ag_gemm_launch_ex(const mk_symm_view* A, const mk_symm_view* ready, const void* B, void* C,
                          int M, int N, int K, int b_layout, uint32_t epoch, void* stream);
 
+/* AllGather + GEMM with a fused SwiGLU epilogue: H[M, N2/2] = silu(X G^T) * (X U^T), where X is
+ * the gathered A and B_gate_up [N2, K] holds, per block of 256 rows, 128 rows of the gate
+ * projection G followed by the 128 rows of the up projection U for the same 128 outputs.
+ * The first half of the tensor-parallel MLP (its second half is mk_gemm_rs_launch on H).  The
+ * reference fuses the same activation into the epilogue of its gate/up GEMM
+ * (src/dispatch_gemm_glu_combine.cu:21-25).  N2 must be a multiple of 256.  H: [W, M/W, N2/2]. */
+int mk_ag_gemm_swiglu_launch(const mk_symm_view* A, const mk_symm_view* ready,
+                             const void* B_gate_up, void* H, int M, int N2, int K, void* stream);
+
 /* GEMM + ReduceScatter.  Replaces gemm_rs_blackwell_prepare / _launch
  * (src/gemm_rs_blackwell.cu:642-732).  A: [M, K_local], B: [N, K_local], C: symmetric [M, N]
  * (workspace: rank s's partial rows of owner o land in slab s of o's copy; after the launch rows
@@ -177,7 +186,10 @@ int mk_op_status_clear(const mk_symm_view* sync, void* stream);
  *      receiver, 1 = an item loads its rows once and stores them to every peer), "push_bulk"
  *      (AllGather push through bulk shared-to-global stores), "ag_lead" (AllGather push pacing:
  *      rows are pushed at most this many quarter raster groups before the GEMM reaches the group
- *      that consumes them; default 6, 0 = push as fast as possible), "max_stages" (cap on the
+ *      that consumes them; default 6, 0 = push as fast as possible), "pdl" (0/1, default 1: launch with
+ *      programmatic stream serialization so a kernel's set-up overlaps the previous kernel's
+ *      tail), "ar_push" (GEMM+AR: 2/1/0 = staging slabs with epoch words / with flags / owners
+ *      fetch partials), "max_stages" (cap on the
  *      operand ring depth, 0 = as many as fit), "l2_promo" (L2 promotion of the operand tensor
  *      maps, 0..3 = none/64/128/256 bytes).  Values are range-checked (wait_limit_ms in
  *      [1, 60000]; only n_comm accepts -1).  The environment variable

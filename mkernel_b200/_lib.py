@@ -86,6 +86,8 @@ _SIGNATURES = {
                                   c_int, c_int, c_int, c_void_p]),
     "mk_ag_gemm_launch_ex": (c_int, [POINTER(SymmView), POINTER(SymmView), c_void_p, c_void_p,
                                      c_int, c_int, c_int, c_int, c_uint32, c_void_p]),
+    "mk_ag_gemm_swiglu_launch": (c_int, [POINTER(SymmView), POINTER(SymmView), c_void_p, c_void_p,
+                                         c_int, c_int, c_int, c_void_p]),
     "mk_gemm_rs_launch_ex": (c_int, [c_void_p, c_void_p, POINTER(SymmView), POINTER(SymmView),
                                      c_int, c_int, c_int, c_int, c_uint32, c_void_p]),
     "mk_gemm_rs_prepare": (c_int, [POINTER(SymmView), c_void_p]),

@@ -142,6 +142,12 @@ __device__ __forceinline__ void stamp_max(const OpParams& p, int slot) {
     atomicMax(p.sync + 24 + slot, static_cast<uint32_t>(global_timer_ns()));
 }
 
+// silu(gate) * up on two fp32 values held as raw bits.
+__device__ __forceinline__ uint32_t silu_mul(uint32_t gate_bits, uint32_t up_bits) {
+  const float g = __uint_as_float(gate_bits);
+  return __float_as_uint(__fdividef(g, 1.0f + __expf(-g)) * __uint_as_float(up_bits));
+}
+
 struct TileInfo {
   int rowblock, q, row0, rows, n0;
 };
@@ -399,11 +405,17 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
     __nv_bfloat16* const c_local = static_cast<__nv_bfloat16*>(p.C);
     __nv_bfloat16* const c_copy =
         (OP == OP_AR && world == 1) ? static_cast<__nv_bfloat16*>(p.peer_out[0]) : nullptr;
-    const bool to_owner = OP == OP_RS && world > 1 && !diag(p, 2);
+    // ReduceScatter through NVSwitch (opt-in): partial tiles stay in this rank's own buffer and
+    // the owner sums all replicas with one switch-side reduction per vector.
+    const bool rs_in_switch = OP == OP_RS && p.use_nvls && p.mc_data != nullptr;
+    const bool to_owner = OP == OP_RS && world > 1 && !rs_in_switch && !diag(p, 2);
     const int slab_mode = OP == OP_AR ? s.ar_push : 0;    // second copy into the owner's slab
     const bool to_slab = slab_mode != 0;
     // bytes per slab row: plain bf16, or (mode 2) every 32-bit word followed by the epoch
     const long long slab_pitch = static_cast<long long>(N) * (slab_mode == 2 ? 4 : 2);
+    // SwiGLU epilogue (plain GEMM and AllGather+GEMM): half as many output columns
+    const bool glu = (OP == OP_GEMM || OP == OP_AG) && p.epilogue == EPI_SWIGLU;
+    const int out_bn = glu ? bn / 2 : bn, n_out = glu ? N / 2 : N;
     const uint32_t tfull0 = bar(BAR_TFULL), stored0 = bar(BAR_STORED);
     const uint32_t tempty0 = CG == 2 ? lead(BAR_TEMPTY) : bar(BAR_TEMPTY);
     for (int t = cta; t < total; t += n_comp) {
@@ -452,6 +464,7 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
           row_ptr[it] = c_local + static_cast<long long>(grow) * ldc;
         }
       }
+      const int n0_out = glu ? ti.n0 / 2 : ti.n0;
       const long long c0 = diag_clock(tr);
       if (!wait_mbar(wc, tfull0 + 8u * acc, acc_phase, 0x500u + acc)) break;
       const long long c1 = diag_clock(tr);
@@ -459,11 +472,24 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
       ptx::tc_fence_after();
       const uint32_t t_base = tmem_base + acc * 256 + (static_cast<uint32_t>(quarter * 32) << 16);
       const uint32_t my_row = stage_buf + lane * 128;
-      for (int c = 0; c < bn; c += 64) {
-        const bool two = c + 32 < bn;
+      for (int c = 0; c < out_bn; c += 64) {
+        const bool two = c + 32 < out_bn;
         uint32_t r0[32], r1[32];
         ptx::tmem_ld_32x32(t_base + c, r0);
         if (two) ptx::tmem_ld_32x32(t_base + c + 32, r1);
+        if (glu) {
+          // Gated activation: the tile's first half of columns is the gate, the second half the
+          // up projection of the same output columns; out = silu(gate) * up, in fp32.
+          uint32_t u[32];
+          ptx::tmem_ld_32x32(t_base + out_bn + c, u);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r0[j] = silu_mul(r0[j], u[j]);
+          ptx::tmem_ld_32x32(t_base + out_bn + c + 32, u);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r1[j] = silu_mul(r1[j], u[j]);
+        }
         ptx::tmem_ld_wait();
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
@@ -486,8 +512,8 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
           }
         }
         __syncwarp();
-        const int col = ti.n0 + c + piece * 8;
-        const bool col_ok = (piece < (two ? 8 : 4)) && (col + 8 <= N);
+        const int col = n0_out + c + piece * 8;
+        const bool col_ok = (piece < (two ? 8 : 4)) && (col + 8 <= n_out);
 #pragma unroll
         for (int it = 0; it < 8; ++it) {
           const int r = it * 4 + sub_row;            // row inside this warp's 32 rows
@@ -769,16 +795,23 @@ __device__ __forceinline__ void reduce_span(const ReduceSpan& sp, int W, uint32_
 }
 
 // AllReduce through NVSwitch: one multimem load returns the fp32-accumulated sum of all replicas.
-__device__ __forceinline__ void reduce_span_nvls(const char* mc_src, char* mc_dst, long long n_vec,
+// kLocalDst: the sums go to this rank's memory with plain stores (ReduceScatter) instead of to
+// every rank through the multicast alias (AllReduce).  U loads are in flight per lane.
+template <bool kLocalDst, int U>
+__device__ __forceinline__ void reduce_span_nvls(const char* mc_src, char* dst, long long n_vec,
                                                  int lane) {
-  for (long long v0 = lane; v0 < n_vec; v0 += 32 * 8) {
-    uint4 v[8];
+  for (long long v0 = lane; v0 < n_vec; v0 += 32 * U) {
+    uint4 v[U];
 #pragma unroll
-    for (int u = 0; u < 8; ++u)
+    for (int u = 0; u < U; ++u)
       if (v0 + u * 32 < n_vec) v[u] = ptx::multimem_ld_reduce_bf16x8(mc_src + (v0 + u * 32) * 16);
 #pragma unroll
-    for (int u = 0; u < 8; ++u)
-      if (v0 + u * 32 < n_vec) ptx::multimem_st_v4(mc_dst + (v0 + u * 32) * 16, v[u]);
+    for (int u = 0; u < U; ++u) {
+      if (v0 + u * 32 < n_vec) {
+        if (kLocalDst) ptx::st_global_v4(dst + (v0 + u * 32) * 16, v[u]);
+        else ptx::multimem_st_v4(dst + (v0 + u * 32) * 16, v[u]);
+      }
+    }
   }
 }
 
@@ -888,6 +921,7 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
   const bool bcast_ag = nvls_ag || (OP == OP_AG && p.ag_fanout != 0);
   const bool nvls_ar = OP == OP_AR && p.use_nvls && !s.one_shot && p.mc_data != nullptr &&
                        p.mc_out != nullptr;
+  const bool nvls_rs = OP == OP_RS && p.use_nvls && p.mc_data != nullptr;
   const long long row_bytes = (OP == OP_AG ? static_cast<long long>(p.K) : static_cast<long long>(s.N)) * 2;
   char* const local = static_cast<char*>(p.peer_data[s.rank]);
   uint32_t entered_mask = 1u << s.rank;  // ranks known to have entered this launch
@@ -1035,8 +1069,12 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
       if (n_vec > 0 && !diag(p, 1)) {
         const long long base = static_cast<long long>(row0) * row_bytes + v_begin * 16;
         if (nvls_ar) {
-          reduce_span_nvls(static_cast<const char*>(p.mc_data) + base,
-                           static_cast<char*>(p.mc_out) + base, n_vec, lane);
+          reduce_span_nvls<false, 8>(static_cast<const char*>(p.mc_data) + base,
+                                     static_cast<char*>(p.mc_out) + base, n_vec, lane);
+        } else if (nvls_rs) {
+          // every rank's partial of these rows sits at the same offset of its own buffer
+          reduce_span_nvls<true, 16>(static_cast<const char*>(p.mc_data) + base, local + base, n_vec,
+                                     lane);
         } else if (ll) {
           const char* src[kMaxWorld];
           char* dst[kMaxWorld];
@@ -1154,11 +1192,6 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
     *s_abort = 0u;
     *s_progress = 0u;
     *s_items_done = 0u;
-    uint32_t e = p.epoch_arg;
-    // The epoch lives on the device (graph replays need no host state) unless the caller
-    // supplies one (GEMM+AR and the multi-node style signatures pass a host epoch)
-    if (p.sync != nullptr && e == 0u) e = ptx::ld_relaxed_sys(p.sync + SW_EPOCH) + 1u;
-    *s_epoch = e;
     if (!is_comm) {
       for (int i = 0; i < kMaxStages; ++i) {
         ptx::mbar_init(bar_base + 8u * (BAR_FULL + i), 1);
@@ -1175,16 +1208,6 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
       ptx::tma_prefetch_desc(&tma_b);
     }
     ptx::fence_mbar_init();
-    if (blockIdx.x == 0) stamp(p, 0);
-    if (blockIdx.x == 0 && p.sync != nullptr && s.world > 1) {
-      // AG / RS: tell every rank that this rank has entered launch e, i.e. that its previous
-      // launch has ended and its buffers may be written again (replaces an all-rank barrier).
-      if (OP == OP_AG || OP == OP_RS)
-        for (int r = 0; r < s.world; ++r) ptx::st_release_sys(p.peer_sync[r] + SW_ENTRY + s.rank, e);
-      // AR: a rank with nothing to reduce still owes its peers the "finished" signal.
-      if (OP == OP_AR && p.n_items <= 0)
-        for (int r = 0; r < s.world; ++r) ptx::st_release_sys(p.peer_sync[r] + SW_EXIT + s.rank, e);
-    }
   }
   if (CG == 2 && !is_comm) ptx::cluster_sync_all();  // both CTAs' barriers exist before any use
   if (!is_comm && warp == 1) {
@@ -1194,6 +1217,30 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
     } else {
       ptx::tmem_alloc_pair(ptx::smem_u32(const_cast<uint32_t*>(s_tmem)), 512);
       ptx::tmem_relinquish_pair();
+    }
+  }
+  // Everything above touched only this CTA's shared and tensor memory, so with a programmatic
+  // dependent launch it overlaps the tail of the previous kernel in the stream.  From here on
+  // global memory is read (epoch, flags, operands the previous kernel may have produced): wait
+  // for the previous kernel to complete, then let the NEXT kernel's CTAs start their own set-up
+  // as SMs become free (they stop at the same wait until this kernel has completed).
+  ptx::grid_dependency_wait();
+  ptx::grid_launch_dependents();
+  if (threadIdx.x == 0) {
+    uint32_t e = p.epoch_arg;
+    // The epoch lives on the device (graph replays need no host state) unless the caller
+    // supplies one (GEMM+AR and the multi-node style signatures pass a host epoch)
+    if (p.sync != nullptr && e == 0u) e = ptx::ld_relaxed_sys(p.sync + SW_EPOCH) + 1u;
+    *s_epoch = e;
+    if (blockIdx.x == 0) stamp(p, 0);
+    if (blockIdx.x == 0 && p.sync != nullptr && s.world > 1) {
+      // AG / RS: tell every rank that this rank has entered launch e, i.e. that its previous
+      // launch has ended and its buffers may be written again (replaces an all-rank barrier).
+      if (OP == OP_AG || OP == OP_RS)
+        for (int r = 0; r < s.world; ++r) ptx::st_release_sys(p.peer_sync[r] + SW_ENTRY + s.rank, e);
+      // AR: a rank with nothing to reduce still owes its peers the "finished" signal.
+      if (OP == OP_AR && p.n_items <= 0)
+        for (int r = 0; r < s.world; ++r) ptx::st_release_sys(p.peer_sync[r] + SW_EXIT + s.rank, e);
     }
   }
   ptx::tc_fence_before();

@@ -5,6 +5,14 @@
 
 namespace mkb {
 
+// Epilogue applied to the accumulator tile before it is stored.
+enum Epilogue : int {
+  EPI_NONE = 0,
+  // Output tile = silu(first half of the tile's columns) * second half: the GEMM's N is twice the
+  // output width and the B rows are laid out [128 gate rows][128 up rows] per 256-wide tile.
+  EPI_SWIGLU = 1,
+};
+
 struct OpParams {
   Sched sched;
   int K;
@@ -20,6 +28,7 @@ struct OpParams {
   int ag_fanout;         // AllGather push: one item loads a row group once, stores it to all peers
   int ring_slots;        // ring depth (16-byte slots per lane) of the in-CTA exchange warp
   int use_nvls;          // exchange through NVSwitch multicast addresses when available
+  int epilogue;          // Epilogue
   int debug_flags;       // timing diagnostics only (results undefined): 1 = exchange workers skip
                          // the data movement but keep the protocol, 2 = RS epilogue stores locally
   uint32_t epoch_arg;    // GEMM+AR: caller-provided epoch; other ops read SW_EPOCH

@@ -55,6 +55,10 @@ struct Options {
   // 2 Mi elements, else as 0); 0 = owners always fetch the partials from their producers.
   long long ar_push = 2;
   long long cta_pair = 1;   // 1: run compute CTAs as pairs (two-SM MMA) when the shape allows
+  // 1: launch with programmatic stream serialization, so that a kernel's set-up (barriers, tensor
+  // memory) overlaps the tail of the previous kernel in the stream; the reference launches the
+  // same way (src/gemm_rs_blackwell.cu:668-680, src/ag_gemm_warp_specialized.cu:678-690).
+  long long pdl = 1;
 };
 static Options g_opt;
 static std::mutex g_opt_mu;
@@ -68,6 +72,7 @@ static long long* option_slot(const char* name) {
   if (!strcmp(name, "group_cols")) return &g_opt.group_cols;
   if (!strcmp(name, "use_nvls")) return &g_opt.use_nvls;
   if (!strcmp(name, "cta_pair")) return &g_opt.cta_pair;
+  if (!strcmp(name, "pdl")) return &g_opt.pdl;
 #ifdef MKB_DIAG
   if (!strcmp(name, "debug_flags")) return &g_opt.debug_flags;
   if (!strcmp(name, "trace_ptr")) return &g_opt.trace_ptr;
@@ -156,7 +161,7 @@ static Options options_snapshot() {
 }
 
 static int make_plan(const Options& o, int op, int rank, int world, int M, int N, int K,
-                     int b_layout, int num_sms, Plan* out) {
+                     int b_layout, int num_sms, Plan* out, int epilogue = EPI_NONE) {
   if (op < OP_GEMM || op > OP_AR) return set_error(MK_ERR_INVALID, "unknown op %d", op);
   if (world < 1 || world > kMaxWorld || rank < 0 || rank >= world)
     return set_error(MK_ERR_INVALID, "rank/world out of range: rank=%d world=%d", rank, world);
@@ -183,6 +188,15 @@ static int make_plan(const Options& o, int op, int rank, int world, int M, int N
                        (long long)m_blocks * ceil_div(N, 128) >= n_comp_max;
   const int quantum = pair_ok ? 128 : (b_layout == MK_B_KN ? 64 : 32);
   int bn = (int)o.block_n;
+  if (epilogue == EPI_SWIGLU) {
+    // a tile is 128 gate columns followed by the 128 up columns of the same outputs
+    if (op != OP_GEMM && op != OP_AG)
+      return set_error(MK_ERR_INVALID, "the SwiGLU epilogue exists for GEMM and AllGather+GEMM only");
+    if (N % 256 != 0 || b_layout != MK_B_NK)
+      return set_error(MK_ERR_INVALID, "SwiGLU epilogue: N=%d must be a multiple of 256 and B "
+                       "stored [N, K] with 128 gate rows then 128 up rows per 256-row block", N);
+    bn = 256;
+  }
   if (bn <= 0) bn = choose_block_n(m_blocks, N, n_comp_max, quantum);
   const int min_q = b_layout == MK_B_KN ? 64 : 32;
   if (bn < 32 || bn > 256 || bn % min_q != 0)
@@ -323,7 +337,7 @@ static int device_sm_count(int* out) {
 
 template <int OP, int CG>
 static int launch_kernel(const Plan& pl, const CUtensorMap& ta, const CUtensorMap& tb,
-                         const OpParams& p, cudaStream_t stream) {
+                         const OpParams& p, cudaStream_t stream, bool pdl) {
   auto kern = fused_gemm_kernel<OP, CG>;
   static bool attr_set[64];
   int dev = 0;
@@ -338,18 +352,22 @@ static int launch_kernel(const Plan& pl, const CUtensorMap& ta, const CUtensorMa
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = pl.smem;
   cfg.stream = stream;
-  cudaLaunchAttribute attr[1];
+  cudaLaunchAttribute attr[2];
+  int n_attr = 0;
   if (CG == 2) {
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 2;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-  } else {
-    cfg.attrs = nullptr;
-    cfg.numAttrs = 0;
+    attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+    attr[n_attr].val.clusterDim.x = 2;
+    attr[n_attr].val.clusterDim.y = 1;
+    attr[n_attr].val.clusterDim.z = 1;
+    ++n_attr;
   }
+  if (pdl) {
+    attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+    ++n_attr;
+  }
+  cfg.attrs = n_attr ? attr : nullptr;
+  cfg.numAttrs = n_attr;
   if (CG == 2) {
     // The kernel is persistent and its roles wait on one another, so every CTA must be resident
     // at once: never launch more pairs than the device can hold (SM counts per GPC need not be
@@ -357,7 +375,9 @@ static int launch_kernel(const Plan& pl, const CUtensorMap& ta, const CUtensorMa
     static int max_pairs[64];
     if (dev < 0 || dev >= 64 || max_pairs[dev] == 0) {
       int n = 0;
-      MKB_CUDA(cudaOccupancyMaxActiveClusters(&n, kern, &cfg));
+      cudaLaunchConfig_t occ = cfg;       // the occupancy query takes the cluster attribute only
+      occ.numAttrs = 1;
+      MKB_CUDA(cudaOccupancyMaxActiveClusters(&n, kern, &occ));
       if (n < 1) return set_error(MK_ERR_CUDA, "device cannot co-schedule a CTA pair");
       if (dev >= 0 && dev < 64) max_pairs[dev] = n;
       if (pl.grid / 2 > n) cfg.gridDim = dim3(2 * n, 1, 1);
@@ -384,6 +404,7 @@ struct OpArgs {
   const mk_symm_view* out;    // AR: C_final
   uint32_t epoch;
   uint32_t* status_only;      // plain GEMM: optional 4 status words
+  int epilogue;               // Epilogue (EPI_NONE unless stated)
 };
 
 static int run_op(const OpArgs& a, cudaStream_t stream) {
@@ -392,7 +413,7 @@ static int run_op(const OpArgs& a, cudaStream_t stream) {
   if (rc != MK_OK) return rc;
   const Options o = options_snapshot();
   Plan pl;
-  rc = make_plan(o, a.op, a.rank, a.world, a.M, a.N, a.K, a.b_layout, sms, &pl);
+  rc = make_plan(o, a.op, a.rank, a.world, a.M, a.N, a.K, a.b_layout, sms, &pl, a.epilogue);
   if (rc != MK_OK) return rc;
 
   OpParams p;
@@ -435,7 +456,8 @@ static int run_op(const OpArgs& a, cudaStream_t stream) {
   p.wait_limit_ns = (uint64_t)o.wait_limit_ms * 1000000ull;
   p.use_nvls = want_nvls ? 1 : 0;
   p.C = a.C;
-  p.ldc = a.N;
+  p.epilogue = a.epilogue;
+  p.ldc = a.epilogue == EPI_SWIGLU ? a.N / 2 : a.N;
   if (a.sync) {
     const long long need = sync_words_needed(pl.sched);
     if ((long long)(a.sync->bytes / 4) < need)
@@ -479,17 +501,17 @@ static int run_op(const OpArgs& a, cudaStream_t stream) {
 
   if (pl.cg == 2) {
     switch (a.op) {
-      case OP_GEMM: return launch_kernel<OP_GEMM, 2>(pl, ta, tb, p, stream);
-      case OP_AG: return launch_kernel<OP_AG, 2>(pl, ta, tb, p, stream);
-      case OP_RS: return launch_kernel<OP_RS, 2>(pl, ta, tb, p, stream);
-      case OP_AR: return launch_kernel<OP_AR, 2>(pl, ta, tb, p, stream);
+      case OP_GEMM: return launch_kernel<OP_GEMM, 2>(pl, ta, tb, p, stream, o.pdl != 0);
+      case OP_AG: return launch_kernel<OP_AG, 2>(pl, ta, tb, p, stream, o.pdl != 0);
+      case OP_RS: return launch_kernel<OP_RS, 2>(pl, ta, tb, p, stream, o.pdl != 0);
+      case OP_AR: return launch_kernel<OP_AR, 2>(pl, ta, tb, p, stream, o.pdl != 0);
     }
   }
   switch (a.op) {
-    case OP_GEMM: return launch_kernel<OP_GEMM, 1>(pl, ta, tb, p, stream);
-    case OP_AG: return launch_kernel<OP_AG, 1>(pl, ta, tb, p, stream);
-    case OP_RS: return launch_kernel<OP_RS, 1>(pl, ta, tb, p, stream);
-    case OP_AR: return launch_kernel<OP_AR, 1>(pl, ta, tb, p, stream);
+    case OP_GEMM: return launch_kernel<OP_GEMM, 1>(pl, ta, tb, p, stream, o.pdl != 0);
+    case OP_AG: return launch_kernel<OP_AG, 1>(pl, ta, tb, p, stream, o.pdl != 0);
+    case OP_RS: return launch_kernel<OP_RS, 1>(pl, ta, tb, p, stream, o.pdl != 0);
+    case OP_AR: return launch_kernel<OP_AR, 1>(pl, ta, tb, p, stream, o.pdl != 0);
   }
   return set_error(MK_ERR_INVALID, "unknown op");
 }
@@ -574,6 +596,25 @@ int mk_ag_gemm_launch_ex(const mk_symm_view* A, const mk_symm_view* ready, const
   a.op = OP_AG; a.A = A->peer[A->rank]; a.a_rows = M; a.B = B; a.C = C;
   a.M = M; a.N = N; a.K = K; a.b_layout = b_layout; a.rank = A->rank; a.world = A->world;
   a.sync = ready; a.data = A; a.epoch = epoch;
+  return run_op(a, static_cast<cudaStream_t>(stream));
+}
+
+int mk_ag_gemm_swiglu_launch(const mk_symm_view* A, const mk_symm_view* ready,
+                             const void* B_gate_up, void* H, int M, int N2, int K, void* stream) {
+  if (!B_gate_up || !H) return set_error(MK_ERR_INVALID, "mk_ag_gemm_swiglu_launch: null operand");
+  if (M < 1 || K < 1 || N2 < 256)
+    return set_error(MK_ERR_INVALID, "mk_ag_gemm_swiglu_launch: bad shape");
+  int rc = check_view(A, "A", (size_t)M * K * 2);
+  if (rc != MK_OK) return rc;
+  rc = check_view(ready, "ready", (size_t)MK_AG_READY_WORDS * 4);
+  if (rc != MK_OK) return rc;
+  if (A->world != ready->world || A->rank != ready->rank)
+    return set_error(MK_ERR_INVALID, "A and ready disagree on rank/world");
+  OpArgs a;
+  memset(&a, 0, sizeof(a));
+  a.op = OP_AG; a.A = A->peer[A->rank]; a.a_rows = M; a.B = B_gate_up; a.C = H;
+  a.M = M; a.N = N2; a.K = K; a.b_layout = MK_B_NK; a.rank = A->rank; a.world = A->world;
+  a.sync = ready; a.data = A; a.epilogue = EPI_SWIGLU;
   return run_op(a, static_cast<cudaStream_t>(stream));
 }
 

@@ -107,6 +107,86 @@ def ag_gemm_warp_specialized_launch(A: DistBuffer, A_copy_ready: DistBuffer, B: 
                                                 _stream()))
 
 
+def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor) -> torch.Tensor:
+    """Weight layout of ``ag_gemm_swiglu_launch``: per block of 256 rows, 128 rows of the gate
+    projection followed by the 128 rows of the up projection of the same outputs.
+    w_gate, w_up: [I, K] with I a multiple of 128 -> [2 I, K]."""
+    I, K = w_gate.shape
+    _require(tuple(w_up.shape) == (I, K) and I % 128 == 0,
+             "w_gate and w_up must both be [I, K] with I a multiple of 128")
+    return torch.stack((w_gate.view(I // 128, 128, K), w_up.view(I // 128, 128, K)),
+                       dim=1).reshape(2 * I, K).contiguous()
+
+
+def ag_gemm_swiglu_launch(A: DistBuffer, A_copy_ready: DistBuffer, B_gate_up: torch.Tensor,
+                          H: torch.Tensor) -> None:
+    """H[d] = silu(A_shard[d] @ G^T) * (A_shard[d] @ U^T) for every shard d: AllGather+GEMM of
+    the gate and up projections with the activation fused into the epilogue (the gated
+    activation never crosses HBM as [M, 2I]).  A: DistBuffer [W, M/W, K]; B_gate_up: [2I, K] from
+    ``interleave_gate_up``; H: [W, M/W, I].  No counterpart call in the reference's TP modules;
+    its MoE kernel fuses the same epilogue (src/dispatch_gemm_glu_combine.cu:21-25)."""
+    _require(isinstance(A, DistBuffer) and isinstance(A_copy_ready, DistBuffer),
+             "A and A_copy_ready must be DistBuffers")
+    _require(A.dtype == torch.bfloat16 and len(A.shape) == 3, "A must be bf16 [W, M/W, K]")
+    _bf16_matrix(B_gate_up, "B_gate_up")
+    W, Ms, K = A.shape
+    N2 = B_gate_up.size(0)
+    _require(B_gate_up.size(1) == K and N2 % 256 == 0,
+             f"B_gate_up must be [2I, K] with K={K} and 2I a multiple of 256")
+    _require(H.dtype == torch.bfloat16 and H.is_cuda and H.is_contiguous() and
+             tuple(H.shape) == (W, Ms, N2 // 2), f"H must be a contiguous bf16 [{W},{Ms},{N2 // 2}]")
+    with _on_device(A.local_rank_):
+        _lib.check(_lib.lib().mk_ag_gemm_swiglu_launch(A.view_ref(), A_copy_ready.view_ref(),
+                                                       B_gate_up.data_ptr(), H.data_ptr(),
+                                                       W * Ms, N2, K, _stream()))
+
+
+class TpMlp:
+    """The tensor-parallel MLP as two fused launches on one stream:
+    AllGather+GEMM(gate, up) with the SwiGLU epilogue -> H, then GEMM+ReduceScatter(down) on H.
+    Both kernels are launched with programmatic stream serialization (the default), so the
+    second one's set-up overlaps the first one's tail; captured in a CUDA graph they are two
+    nodes.  All buffers are allocated once, collectively (same order on every rank):
+      x:    DistBuffer [W, M/W, K]    rank r fills x.data_[r]
+      out:  rows [rank*M/W, (rank+1)*M/W) of y.data_ (the reduced slice)"""
+
+    def __init__(self, M: int, K: int, I_local: int, N_out: int, local_rank: int,
+                 local_world_size: int):
+        W = int(local_world_size)
+        _require(M % W == 0, "M must be divisible by the world size")
+        dev = torch.device("cuda", local_rank)
+        self.M, self.K, self.I, self.N, self.W, self.rank = M, K, I_local, N_out, W, local_rank
+        self.x = DistBuffer((W, M // W, K), torch.bfloat16, local_rank, W)
+        self.ready = DistBuffer((ag_gemm_warp_specialized_ready_words,), torch.int32, local_rank, W)
+        self.ready.data_.zero_()
+        self.h = torch.empty((W, M // W, I_local), device=dev, dtype=torch.bfloat16)
+        self.y = DistBuffer((M, N_out), torch.bfloat16, local_rank, W)
+        self.sync = DistBuffer(gemm_rs_blackwell_sync_shape, torch.int32, local_rank, W)
+        gemm_rs_blackwell_prepare(None, None, self.y, self.sync)
+        self.w_gate_up = None
+        self.w_down = None
+
+    def load_weights(self, w_gate: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor) -> None:
+        """w_gate, w_up: [I_local, K]; w_down: [N_out, I_local] (this rank's shards)."""
+        self.w_gate_up = interleave_gate_up(w_gate, w_up)
+        _bf16_matrix(w_down, "w_down")
+        _require(tuple(w_down.shape) == (self.N, self.I), f"w_down must be [{self.N},{self.I}]")
+        self.w_down = w_down
+
+    def forward(self) -> torch.Tensor:
+        """Enqueue both launches on the current stream; returns the view of this rank's output
+        rows (valid when the stream has completed)."""
+        ag_gemm_warp_specialized_prepare(self.ready, self.M, 2 * self.I)
+        ag_gemm_swiglu_launch(self.x, self.ready, self.w_gate_up, self.h)
+        gemm_rs_blackwell_launch(self.h.view(self.M, self.I), self.w_down, self.y, self.sync)
+        Ms = self.M // self.W
+        return self.y.data_[self.rank * Ms:(self.rank + 1) * Ms]
+
+    def free(self) -> None:
+        for b in (self.x, self.ready, self.y, self.sync):
+            b.free()
+
+
 def gemm_rs_blackwell_prepare(A, B, C: DistBuffer, sync: DistBuffer) -> None:
     """Zero the synchronisation words once; the caller then synchronises and barriers."""
     _require(isinstance(sync, DistBuffer), "sync must be a DistBuffer")

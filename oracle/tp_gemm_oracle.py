@@ -10,6 +10,7 @@ with torch.matmul + torch.distributed collectives on seeded inputs):
   GEMM+ReduceScatter out_r = (sum_s A_s @ B_s^T)[r*M/W:(r+1)*M/W] bench/gemm_rs_bench.py:408-410, 433-435
   GEMM+AllReduce    C = sum_s A_s @ B_s on every rank             bench/gemm_ar_blackwell_bench.py:423-438
   acceptance        three-tier check_close                        bench/common.py:312-367
+  TP MLP chain      AG+GEMM(gate, up) -> SwiGLU -> GEMM+RS(down)  the two operators back to back
 
 Arithmetic contract: operands are bf16 values; products and sums are taken in fp32 (or fp64 with
 ``exact=True``) over the bf16-rounded operands; results are compared before any rounding of the
@@ -104,6 +105,44 @@ def gemm_ar_ref(A_list: Sequence[torch.Tensor], B_kn_list: Sequence[torch.Tensor
     for p in partials[1:]:
         total = total + p
     return total, partials
+
+
+def interleave_gate_up(w_gate: torch.Tensor, w_up: torch.Tensor, block: int = 128) -> torch.Tensor:
+    """Row layout the fused SwiGLU epilogue expects for the up-projection weights: blocks of
+    `block` gate rows followed by the `block` up rows of the same output columns, so that one
+    2*block-wide output tile of the GEMM holds matching gate and up columns.
+    w_gate, w_up: [I, K] -> [2I, K].  I must be a multiple of `block`."""
+    I, K = w_gate.shape
+    assert w_up.shape == (I, K) and I % block == 0
+    g = w_gate.view(I // block, block, K)
+    u = w_up.view(I // block, block, K)
+    return torch.stack((g, u), dim=1).reshape(2 * I, K).contiguous()
+
+
+def tp_mlp_ref(x_shards: Sequence[torch.Tensor], w_gate_list: Sequence[torch.Tensor],
+               w_up_list: Sequence[torch.Tensor], w_down_list: Sequence[torch.Tensor],
+               exact: bool = False):
+    """The tensor-parallel MLP the two fused operators form back to back (the reference's fused
+    gate/up GEMM + SwiGLU epilogue is described at src/dispatch_gemm_glu_combine.cu:21-25; its
+    AllGather+GEMM and GEMM+ReduceScatter are the operators above):
+        x   = cat_r(x_r)                                  gathered rows, [M, K]
+        h_s = silu(x @ w_gate_s^T) * (x @ w_up_s^T)       rank s's columns, [M, I/W], stored bf16
+        out = (sum_s h_s @ w_down_s^T)[r*M/W:(r+1)*M/W]   row-scattered, [M/W, N] per rank
+    w_gate_s, w_up_s: [I/W, K]; w_down_s: [N, I/W].  Returns (out per rank, [h_s as bf16])."""
+    x = torch.cat(list(x_shards), dim=0)
+    dt = torch.float64 if exact else torch.float32
+    hs, total = [], None
+    for wg, wu, wd in zip(w_gate_list, w_up_list, w_down_list):
+        g = x.to(dt) @ wg.to(dt).t()
+        u = x.to(dt) @ wu.to(dt).t()
+        h = (g * torch.sigmoid(g) * u).to(torch.bfloat16)     # h crosses HBM as bf16
+        hs.append(h)
+        p = h.to(dt) @ wd.to(dt).t()
+        total = p if total is None else total + p
+    W = len(hs)
+    M = total.shape[0]
+    assert M % W == 0
+    return [total[r * (M // W):(r + 1) * (M // W)] for r in range(W)], hs
 
 
 # ---------------------------------------------------------------------------------------------

@@ -373,7 +373,54 @@ def case_graph(rank, world, M, N, K, seed, replays, max_rows):
     return res
 
 
-CASES = {"ag": case_ag, "rs": case_rs, "ar": case_ar, "compat": case_compat, "graph": case_graph}
+def case_mlp(rank, world, M, K, I, N, seed, iters, max_rows):
+    """The tensor-parallel MLP: AllGather+GEMM(gate, up) with the SwiGLU epilogue, then
+    GEMM+ReduceScatter(down), two launches back to back with no host synchronisation between."""
+    from mkernel_b200 import ops
+    dev = torch.device("cuda", rank)
+    Ms, Il = M // world, I // world
+    g = torch.Generator().manual_seed(seed)
+    xs = [torch.randn((Ms, K), generator=g).to(torch.bfloat16) for _ in range(world)]
+    wgs = [(torch.randn((Il, K), generator=g) / K ** 0.5).to(torch.bfloat16) for _ in range(world)]
+    wus = [(torch.randn((Il, K), generator=g) / K ** 0.5).to(torch.bfloat16) for _ in range(world)]
+    wds = [(torch.randn((N, Il), generator=g) / I ** 0.5).to(torch.bfloat16) for _ in range(world)]
+    rows = _sample_rows(Ms, max_rows, seed)
+    x_full = torch.cat(xs, 0)
+    grow = rank * Ms + rows
+    ref = scale = None
+    h_mine = None
+    for s_ in range(world):
+        gate = x_full.float() @ wgs[s_].float().t()
+        up = x_full.float() @ wus[s_].float().t()
+        h = (gate * torch.sigmoid(gate) * up).to(torch.bfloat16)
+        if s_ == rank:
+            h_mine = h
+        p = h[grow].float() @ wds[s_].float().t()
+        ref = p if ref is None else ref + p
+        scale = p.abs() if scale is None else scale + p.abs()
+    mlp = ops.TpMlp(M, K, Il, N, rank, world)
+    mlp.load_weights(wgs[rank].to(dev), wus[rank].to(dev), wds[rank].to(dev))
+    mlp.x.data_.zero_()
+    mlp.x.data_[rank].copy_(xs[rank])
+    sync_all()
+    res = dict(op="mlp", M=M, N=N, K=K, rel=[], rel_plain=[], rel_h=[], status=[], gathered_exact=[])
+    for it in range(iters):
+        y = mlp.forward()
+        torch.cuda.synchronize()
+        res["status"].append(list(ops.op_status(mlp.ready)))
+        res["status"].append(list(ops.op_status(mlp.sync)))
+        res["gathered_exact"].append(bool(torch.equal(mlp.x.data_.view(M, K).cpu(), x_full)))
+        res["rel_h"].append(orc.rel_error(mlp.h.view(M, Il).cpu(), h_mine.float()))
+        res["rel"].append(orc.rel_error(y[rows.to(dev)].cpu(), ref, scale))
+        res["rel_plain"].append(orc.rel_error(y[rows.to(dev)].cpu(), ref))
+        dist.barrier()
+    sync_all()
+    mlp.free()
+    return res
+
+
+CASES = {"ag": case_ag, "rs": case_rs, "ar": case_ar, "compat": case_compat, "graph": case_graph,
+         "mlp": case_mlp}
 
 
 def run_rank(rank: int, world: int, port: int, key: str, cases: list, out_dir: str, options=None):

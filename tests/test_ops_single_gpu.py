@@ -201,3 +201,44 @@ def test_multinode_signatures_on_one_gpu():
                          1, 0, 8, 0, 0, 1, trace_slot=-1)
     torch.cuda.synchronize()
     assert orc.rel_error(C3f.data_.cpu(), orc.gemm_ar_ref([a], [b_kn])[0]) <= orc.REL_TOL
+
+
+def test_swiglu_epilogue_and_mlp_chain_world1():
+    """AllGather+GEMM(gate, up) with the fused SwiGLU epilogue, then GEMM+ReduceScatter(down), on
+    one GPU: H within the tolerance of the oracle's fp32 activation (rounded once to bf16), the
+    chain's output within the tolerance of an oracle that also stores H as bf16."""
+    from mkernel_b200 import ops
+    torch.cuda.set_device(0)
+    M, K, I, N = 384, 320, 256, 264
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn((M, K), generator=g).to(torch.bfloat16)
+    wg = (torch.randn((I, K), generator=g) / K ** 0.5).to(torch.bfloat16)
+    wu = (torch.randn((I, K), generator=g) / K ** 0.5).to(torch.bfloat16)
+    wd = (torch.randn((N, I), generator=g) / I ** 0.5).to(torch.bfloat16)
+    mlp = ops.TpMlp(M, K, I, N, 0, 1)
+    mlp.load_weights(wg.to(DEV), wu.to(DEV), wd.to(DEV))
+    mlp.x.data_[0].copy_(x)
+    assert torch.equal(mlp.w_gate_up.cpu(), orc.interleave_gate_up(wg, wu))
+    outs, hs = orc.tp_mlp_ref([x], [wg], [wu], [wd])
+    for _ in range(2):                      # second pass: epochs advance, nothing is reset
+        mlp.h.zero_()
+        y = mlp.forward()
+        torch.cuda.synchronize()
+        assert ops.op_status(mlp.ready)[0] == 0 and ops.op_status(mlp.sync)[0] == 0
+        # the activation: fp32 silu(g) * u rounded once to bf16 (fast exp/divide on the device)
+        assert orc.rel_error(mlp.h.view(M, I).cpu(), hs[0].float()) <= orc.REL_TOL
+        assert orc.rel_error(y.cpu(), outs[0]) <= orc.REL_TOL
+    mlp.free()
+
+
+def test_swiglu_rejects_widths_that_split_a_gate_up_block():
+    from mkernel_b200 import ops
+    mod = mkernel_b200.load("ag_gemm_warp_specialized")
+    A = mod.DistBuffer((1, 128, 64), dtype=torch.bfloat16, local_rank=0, local_world_size=1)
+    ready = mod.DistBuffer((mod.ag_gemm_warp_specialized_ready_words,), dtype=torch.int32,
+                           local_rank=0, local_world_size=1)
+    ready.data_.zero_()
+    B = torch.zeros((384, 64), device=DEV, dtype=torch.bfloat16)      # 2I = 384: not 256-aligned
+    H = torch.zeros((1, 128, 192), device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError):
+        ops.ag_gemm_swiglu_launch(A, ready, B, H)

@@ -41,7 +41,10 @@ def _rank(rank, world, port, q):
     ar = a.float() @ b.float()
     dist.all_reduce(ar)
     out["ar"] = ar
-    q.put((rank, out))
+    # Tensors travel by value (raw bytes), not as shared-memory handles: a handle is only valid
+    # while this process lives, and the parent may read the queue after it has exited.
+    q.put((rank, {k: (str(v.dtype), tuple(v.shape), v.contiguous().view(torch.uint8).numpy().tobytes())
+                  for k, v in out.items()}))
     dist.barrier()
     dist.destroy_process_group()
 
@@ -55,7 +58,12 @@ def test_gloo_ranks_match_oracle():
     procs = [ctx.Process(target=_rank, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
-    got = dict(q.get(timeout=180) for _ in range(world))
+    got = {}
+    for _ in range(world):
+        rank, packed = q.get(timeout=180)
+        got[rank] = {k: torch.frombuffer(bytearray(raw), dtype=torch.uint8)
+                     .view(getattr(torch, dt.split(".")[1])).view(shape)
+                     for k, (dt, shape, raw) in packed.items()}
     for p in procs:
         p.join(60)
     # config 1 against an fp64 evaluation
