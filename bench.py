@@ -621,6 +621,19 @@ def run_ours(args):
         rec["graph_error"] = repr(e)[:200]
     ops_out["gemm_ar"] = rec
 
+    C4.free(); C4f.free(); bar4.free()
+    del A4, B4, c4
+    A.free(); ready.free()
+    del B, C
+    torch.cuda.empty_cache()
+
+    # ---------------- in-switch ReduceScatter variant (opt-in), against the default ----------------
+    if W > 1:
+        ops_out["gemm_rs"]["in_switch_variant"] = rs_in_switch_record(dst, rs, _lib, sub_steps)
+
+    # ---------------- TP MLP chain: AG+GEMM(gate, up)+SwiGLU -> GEMM+RS(down) ----------------
+    ops_out["mlp_chain"] = mlp_chain_record(dst, ops, peaks, sub_steps)
+
     traffic = NCU_TRAFFIC_BYTES_PER_LAUNCH if W == 1 else None
     line = {
         "metric": "fused AG-GEMM TFLOPS (whole job; GEMM-RS / GEMM-AR under ops)",
@@ -647,7 +660,7 @@ def run_ours(args):
                 "outputs_match_device_result": e2e_ok},
         "gpu_launches": steps,
         "clocks": sampler.summary(),
-        "parity": {k: v["parity"]["ok"] for k, v in ops_out.items()},
+        "parity": {k: v["parity"]["ok"] for k, v in ops_out.items() if "parity" in v},
         "ops": ops_out,
         "plan": plan_summary(_lib, W, rank),
     }
@@ -661,6 +674,146 @@ def run_ours(args):
         dst.dist.destroy_process_group()
     if not all_ok:
         raise SystemExit("parity check failed: see the 'parity' records of the line above")
+
+
+def rs_in_switch_record(dst, rs, _lib, steps):
+    """GEMM+ReduceScatter with the partials left in place and summed by the NVSwitch
+    (multimem.ld_reduce) instead of pushed into the owner's slabs and summed by SMs: time and
+    error figure next to the default's.  Needs buffers with a multicast alias."""
+    W, rank, dev = dst.world, dst.local_rank, dst.device
+    M3, N3, K3 = CFG3["M"], CFG3["N"], CFG3["K"]
+    A3 = randn_bf16((M3, K3), 2 + rank, dev)
+    B3 = randn_bf16((N3, K3), 202 + rank, dev, (K3 * W) ** -0.5)
+    try:
+        C3 = rs.DistBuffer((M3, N3), dtype=torch.bfloat16, local_rank=rank, local_world_size=W,
+                           multicast=True)
+    except Exception as e:
+        return {"unavailable": repr(e)[:160]}
+    sync3 = rs.DistBuffer(rs.gemm_rs_blackwell_sync_shape, dtype=torch.int32, local_rank=rank,
+                          local_world_size=W)
+    rs.gemm_rs_blackwell_prepare(A3, B3, C3, sync3)
+    dst.barrier()
+    rec = {"multicast": bool(C3.multicast_enabled)}
+    if C3.multicast_enabled:
+        def step(i, e0, e1):
+            e0.record()
+            rs.gemm_rs_blackwell_launch(A3, B3, C3, sync3)
+            e1.record()
+        for name, flag in (("default_ms", 0), ("in_switch_ms", 1)):
+            _lib.set_option("use_nvls", flag)
+            dst.barrier()
+            _, rec[name] = timed_loop(dst, step, steps, 3)
+        # error figure of the in-switch path (its sum is not rounded to nearest)
+        Ms3 = M3 // W
+        part = A3.float() @ B3.float().t()
+        scale = sum_over_ranks(dst, part.abs())[rank * Ms3:(rank + 1) * Ms3].clone()
+        ref = sum_over_ranks(dst, part)[rank * Ms3:(rank + 1) * Ms3]
+        f = error_figures(C3.data_[rank * Ms3:(rank + 1) * Ms3], ref, scale)
+        rec["in_switch_rel"] = dst.max_over_ranks(f["rel"])
+        rec["in_switch_rel_plain"] = dst.max_over_ranks(f["rel_plain"])
+        _lib.set_option("use_nvls", 0)
+        rs.op_status(sync3)
+        del part, ref, scale
+    dst.barrier()
+    C3.free(); sync3.free()
+    return rec
+
+
+def mlp_chain_record(dst, ops, peaks, steps):
+    """Llama-70B MLP with TP = n_gpus (I_local = 3584 per GPU): the fused chain (two launches:
+    AllGather+GEMM of gate and up with the SwiGLU epilogue, GEMM+ReduceScatter of down) against
+    the same two operators with the activation as a separate elementwise kernel, and against the
+    unfused cuBLAS + NCCL chain."""
+    W, rank, dev = dst.world, dst.local_rank, dst.device
+    M, K, I, N = 8192, 8192, 3584, 8192
+    Ms = M // W
+    mlp = ops.TpMlp(M, K, I, N, rank, W)
+    wg = randn_bf16((I, K), 701 + rank, dev, K ** -0.5)
+    wu = randn_bf16((I, K), 801 + rank, dev, K ** -0.5)
+    wd = randn_bf16((N, I), 901 + rank, dev, (I * W) ** -0.5)
+    mlp.load_weights(wg, wu, wd)
+    mlp.x.data_.zero_()
+    mlp.x.data_[rank].copy_(randn_bf16((Ms, K), 601 + rank, dev))
+    dst.barrier()
+
+    def fused(i, e0, e1):
+        e0.record()
+        mlp.forward()
+        e1.record()
+
+    _, fused_ms = timed_loop(dst, fused, steps, 3)
+    ops.op_status(mlp.ready); ops.op_status(mlp.sync)
+    # parity of the chain (untimed): fp32 products of the same bf16 operands, H stored as bf16
+    y = mlp.forward()
+    dst.barrier()
+    x_full = torch.cat([randn_bf16((Ms, K), 601 + r, dev) for r in range(W)], 0)
+    gate = x_full.float() @ wg.float().t()
+    gate = gate * torch.sigmoid(gate)
+    gate *= x_full.float() @ wu.float().t()
+    h_ref = gate.to(torch.bfloat16)
+    del gate
+    rel_h = error_figures(mlp.h.view(M, I), h_ref.float())["rel"]
+    part = h_ref.float() @ wd.float().t()
+    scale = sum_over_ranks(dst, part.abs())[rank * Ms:(rank + 1) * Ms].clone()
+    ref = sum_over_ranks(dst, part)[rank * Ms:(rank + 1) * Ms]
+    f = error_figures(y, ref, scale)
+    parity = {"rel": dst.max_over_ranks(f["rel"]), "rel_plain": dst.max_over_ranks(f["rel_plain"]),
+              "rel_activation": dst.max_over_ranks(rel_h),
+              "gathered_exact": bool(torch.equal(mlp.x.data_.view(M, K), x_full)),
+              "tolerance": PARITY_TOL}
+    parity["ok"] = bool(parity["rel"] <= PARITY_TOL and parity["rel_activation"] <= PARITY_TOL and
+                        parity["gathered_exact"])
+    del part, ref, scale, h_ref, x_full
+
+    # the same two operators, activation as its own kernel on [M, 2I]
+    gu = torch.empty((W, Ms, 2 * I), device=dev, dtype=torch.bfloat16)
+
+    def separate(i, e0, e1):
+        e0.record()
+        ops.ag_gemm_warp_specialized_prepare(mlp.ready, M, 2 * I)
+        ops.ag_gemm_warp_specialized_launch(mlp.x, mlp.ready, mlp.w_gate_up, gu)
+        g4 = gu.view(M, I // 128, 2, 128)
+        torch.mul(torch.nn.functional.silu(g4[:, :, 0]), g4[:, :, 1], out=mlp.h.view(M, I // 128, 128))
+        ops.gemm_rs_blackwell_launch(mlp.h.view(M, I), mlp.w_down, mlp.y, mlp.sync)
+        e1.record()
+
+    _, sep_ms = timed_loop(dst, separate, steps, 3)
+    ops.op_status(mlp.ready); ops.op_status(mlp.sync)
+    del gu
+    # unfused: NCCL all-gather, cuBLAS, elementwise, cuBLAS, NCCL reduce-scatter
+    x_all = torch.empty((M, K), device=dev, dtype=torch.bfloat16)
+    g_u = torch.empty((M, 2 * I), device=dev, dtype=torch.bfloat16)
+    hh = torch.empty((M, I), device=dev, dtype=torch.bfloat16)
+    yy = torch.empty((M, N), device=dev, dtype=torch.bfloat16)
+    y_rs = torch.empty((Ms, N), device=dev, dtype=torch.bfloat16)
+    w_cat = torch.cat((wg, wu), 0)
+
+    def unfused(i, e0, e1):
+        e0.record()
+        if W > 1:
+            dst.dist.all_gather_into_tensor(x_all, mlp.x.data_[rank])
+            torch.matmul(x_all, w_cat.t(), out=g_u)
+        else:
+            torch.matmul(mlp.x.data_[rank], w_cat.t(), out=g_u)
+        torch.mul(torch.nn.functional.silu(g_u[:, :I]), g_u[:, I:], out=hh)
+        torch.mm(hh, wd.t(), out=yy)
+        if W > 1:
+            dst.dist.reduce_scatter_tensor(y_rs, yy)
+        e1.record()
+
+    _, unf_ms = timed_loop(dst, unfused, steps, 3)
+    flops = 2.0 * M * (2 * I) * K + 2.0 * M * N * I
+    nvlink = (W - 1) / W * (M * K + M * N) * 2
+    t_roof = max(flops / (peaks["bf16_tflops"] * 1e12), nvlink / (NVLINK_GBS * 1e9)) * 1e3
+    rec = {"name": "TP MLP chain (AG+GEMM gate/up + SwiGLU -> GEMM+RS down)",
+           "shape": {"M": M, "K": K, "I_per_gpu": I, "N": N}, "tp": W,
+           "fused_ms": fused_ms, "separate_activation_ms": sep_ms, "unfused_ms": unf_ms,
+           "speedup_vs_separate": sep_ms / fused_ms, "speedup_vs_unfused": unf_ms / fused_ms,
+           "tflops_per_gpu": flops / (fused_ms * 1e-3) / 1e12,
+           "fused_roofline_ms": t_roof, "fused_roofline_frac": t_roof / fused_ms,
+           "launches_per_step": 2, "parity": parity}
+    mlp.free()
+    return rec
 
 
 def headline_config(W):
