@@ -189,7 +189,10 @@ int mk_op_status_clear(const mk_symm_view* sync, void* stream);
  *      that consumes them; default 6, 0 = push as fast as possible), "pdl" (0/1, default 1: launch with
  *      programmatic stream serialization so a kernel's set-up overlaps the previous kernel's
  *      tail), "ar_push" (GEMM+AR: 2/1/0 = staging slabs with epoch words / with flags / owners
- *      fetch partials), "max_stages" (cap on the
+ *      fetch partials), "split_tail" (0/1, default 1: cut the tiles
+ *      of a partial last round along K over all CTAs -- plain GEMM and AllGather+GEMM; uses a
+ *      scratch buffer per device and stream that the library allocates at the first such launch,
+ *      never during stream capture), "max_stages" (cap on the
  *      operand ring depth, 0 = as many as fit), "l2_promo" (L2 promotion of the operand tensor
  *      maps, 0..3 = none/64/128/256 bytes).  Values are range-checked (wait_limit_ms in
  *      [1, 60000]; only n_comm accepts -1).  The environment variable

@@ -142,6 +142,67 @@ __device__ __forceinline__ void stamp_max(const OpParams& p, int slot) {
     atomicMax(p.sync + 24 + slot, static_cast<uint32_t>(global_timer_ns()));
 }
 
+// ------------------------------------------------------------------------------------------
+// Work of one compute CTA: whole tiles, then at most one piece of a tail tile.
+// ------------------------------------------------------------------------------------------
+// Tiles are handed out round-robin (tile t to CTA t mod n_comp), so the last round is usually
+// partial: with 6.05 rounds of tiles the 7th keeps 5 % of the CTAs busy for a whole tile time.
+// When splitting is enabled (plain GEMM and AllGather+GEMM), the tiles of a partial last round
+// are instead cut along K into `parts` pieces, one per CTA (CTA pair), so that every CTA gets a
+// share of that round; the pieces' fp32 accumulators go through a scratch buffer and are summed
+// in a fixed order (deterministic), each CTA finishing a slice of rows of its tile.
+struct SplitPlan {
+  int full_rounds;   // rounds in which every CTA has a whole tile
+  int rem_units;     // tail tiles (pair tiles for CG = 2) = units of the partial round
+  int parts;         // pieces per tail tile; 0 = no splitting (the partial round runs whole tiles)
+};
+template <int CG>
+__device__ __forceinline__ SplitPlan make_split(const OpParams& p, int total_tiles, int n_comp) {
+  SplitPlan sp;
+  sp.full_rounds = 0; sp.rem_units = 0; sp.parts = 0;
+  if (p.split_max_parts < 2 || p.split_scratch == nullptr) return sp;
+  const int units = n_comp / CG, unit_tiles = total_tiles / CG;
+  const int full = unit_tiles / units, rem = unit_tiles % units;
+  if (full < 1 || rem == 0 || rem > units / 2) return sp;
+  int parts = units / rem;
+  if (parts > p.split_max_parts) parts = p.split_max_parts;
+  if (parts > p.k_blocks / 4) parts = p.k_blocks / 4;
+  if (parts < 2) return sp;
+  sp.full_rounds = full; sp.rem_units = rem; sp.parts = parts;
+  return sp;
+}
+struct WorkItem {
+  int t;          // tile index in visiting order
+  int kb0, kb1;   // k-blocks [kb0, kb1)
+  int piece;      // -1: the whole tile; else tail tile * parts + part
+};
+// `cta` = index of this CTA among the compute CTAs, `it` = 0, 1, 2, ... ; false when done.
+template <int CG>
+__device__ __forceinline__ bool work_item(const OpParams& p, const SplitPlan& sp, int total_tiles,
+                                          int n_comp, int cta, int it, WorkItem& w) {
+  w.kb0 = 0; w.kb1 = p.k_blocks; w.piece = -1;
+  if (sp.parts == 0) {
+    w.t = cta + it * n_comp;
+    return w.t < total_tiles;
+  }
+  if (it < sp.full_rounds) { w.t = cta + it * n_comp; return true; }
+  if (it > sp.full_rounds) return false;
+  const int unit = cta / CG;
+  if (unit >= sp.rem_units * sp.parts) return false;
+  const int j = unit / sp.parts, i = unit % sp.parts;
+  w.t = sp.full_rounds * n_comp + j * CG + (cta % CG);
+  w.kb0 = static_cast<int>(static_cast<long long>(i) * p.k_blocks / sp.parts);
+  w.kb1 = static_cast<int>(static_cast<long long>(i + 1) * p.k_blocks / sp.parts);
+  w.piece = unit;
+  return true;
+}
+// Scratch layout of one piece of one CTA (128 rows x block_n fp32): 16-byte vectors in the order
+// [32-column chunk][vector of the chunk (8)][row (128)], so that the epilogue's stores (thread =
+// row) and the slice sums (consecutive threads = consecutive rows) are both coalesced.
+__device__ __forceinline__ long long split_vec_offset(int col4, int row) {   // col4 = column / 4
+  return (static_cast<long long>(col4) * kBlockM + row) * 16;
+}
+
 // silu(gate) * up on two fp32 values held as raw bits.
 __device__ __forceinline__ uint32_t silu_mul(uint32_t gate_bits, uint32_t up_bits) {
   const float g = __uint_as_float(gate_bits);
@@ -207,6 +268,9 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
   // Barriers the pair shares live in the leader CTA.
   auto lead = [&](int slot) { return CG == 2 ? ptx::map_to_cta(bar(slot), 0) : bar(slot); };
   constexpr bool kSignals = (OP == OP_RS || OP == OP_AR);
+  SplitPlan split;
+  split.full_rounds = 0; split.rem_units = 0; split.parts = 0;
+  if (OP == OP_GEMM || OP == OP_AG) split = make_split<CG>(p, total, n_comp);
   // Diagnostics build: p.trace set = coarse counters (kernel and MMA-loop cycles); flag 256 adds
   // a cycle-counter read around every wait, which itself slows the MMA issue loop.
   const bool trc = kDiag && p.trace != nullptr;
@@ -218,7 +282,7 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
     // is read through a reference, and every barrier / TMA instruction below is a compiler
     // memory barrier, so a field left in the block would be re-read once per use.
     wc.where = (blockIdx.x << 8) | 0u;
-    const int k_blocks = p.k_blocks, stages = p.stages;
+    const int stages = p.stages;
     const bool b_mn = p.b_mn_major != 0;
     const bool no_loads = diag(p, 64), idle = diag(p, 1024);
     const uint32_t full0 = CG == 2 ? lead(BAR_FULL) : bar(BAR_FULL);   // + 8 * stage
@@ -229,7 +293,9 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
     uint32_t phase = 0;
     bool ok = true;
     long long tr_empty = 0, tr_gather = 0;
-    for (int t = cta; t < total && ok; t += n_comp) {
+    WorkItem w;
+    for (int it = 0; ok && work_item<CG>(p, split, total, n_comp, cta, it, w); ++it) {
+      const int t = w.t;
       const TileInfo ti = tile_info(s, t);
       if (OP == OP_AG && lane == 0) *s_progress = static_cast<uint32_t>(t);
       if (OP == OP_AG && s.world > 1 && rowblock_shard(s, ti.rowblock) != s.rank) {
@@ -247,8 +313,8 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
       if (lane == 0 && !idle) {
         const int row0 = ti.row0;
         const int nb0 = ti.n0 + crank * b_rows;   // first B row (C column) this CTA loads
-        int kx = 0;                                // element offset of the k-block
-        for (int kb = 0; kb < k_blocks; ++kb, kx += kBlockK) {
+        int kx = w.kb0 * kBlockK;                  // element offset of the k-block
+        for (int kb = w.kb0; kb < w.kb1; ++kb, kx += kBlockK) {
           const long long c0 = diag_clock(tr);
           if (!wait_mbar(wc, empty0 + 8u * stage, phase ^ 1u, 0x100u + stage)) { ok = false; break; }
           tr_empty += diag_clock(tr) - c0;
@@ -300,7 +366,7 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
     // that elects its issuing lane and advances the descriptors by adding to their low word.
     wc.where = (blockIdx.x << 8) | 1u;
     if (crank == 0) {
-      const int k_blocks = p.k_blocks, stages = p.stages;
+      const int stages = p.stages;
       const bool b_mn = p.b_mn_major != 0;
       const uint32_t idesc = ptx::make_idesc_bf16(bn, b_mn ? 1u : 0u, 128u * CG);
       const uint32_t desc_hi = static_cast<uint32_t>(ptx::make_smem_desc_sw128(0, 0, 1024) >> 32);
@@ -323,7 +389,8 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
       bool ok = true;
       long long tr_tiles = 0;
       const long long tr_begin = diag_clock(trc);
-      for (int t = cta; t < total; t += n_comp) {
+      WorkItem w;
+      for (int it = 0; work_item<CG>(p, split, total, n_comp, cta, it, w); ++it) {
         if (!__all_sync(0xffffffffu,
                         wait_mbar(wc, bar(BAR_TEMPTY + acc), acc_phase ^ 1u, 0x200u + acc)))
           break;
@@ -331,7 +398,7 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
         ptx::tc_fence_after();
         const uint32_t d_tmem = d_base + acc * 256;
         uint32_t accumulate = 0u;
-        for (int kb = 0; kb < k_blocks; ++kb) {
+        for (int kb = w.kb0; kb < w.kb1; ++kb) {
           if (!(kDiag && no_full_wait) &&
               !__all_sync(0xffffffffu, wait_mbar(wc, full0 + 8u * stage, phase, 0x300u + stage))) {
             ok = false;
@@ -418,8 +485,88 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
     const int out_bn = glu ? bn / 2 : bn, n_out = glu ? N / 2 : N;
     const uint32_t tfull0 = bar(BAR_TFULL), stored0 = bar(BAR_STORED);
     const uint32_t tempty0 = CG == 2 ? lead(BAR_TEMPTY) : bar(BAR_TEMPTY);
-    for (int t = cta; t < total; t += n_comp) {
+    WorkItem w;
+    for (int wi = 0; work_item<CG>(p, split, total, n_comp, cta, wi, w); ++wi) {
+      const int t = w.t;
       const TileInfo ti = tile_info(s, t);
+      if ((OP == OP_GEMM || OP == OP_AG) && w.piece >= 0) {
+        // ---- a piece of a tail tile: fp32 partial -> scratch; then sum a slice of the tile ----
+        if (!wait_mbar(wc, tfull0 + 8u * acc, acc_phase, 0x500u + acc)) break;
+        ptx::tc_fence_after();
+        const uint32_t t_base = tmem_base + acc * 256 + (static_cast<uint32_t>(quarter * 32) << 16);
+        const long long slot_bytes = static_cast<long long>(kBlockM) * bn * 4;
+        char* const scratch = reinterpret_cast<char*>(p.split_scratch);
+        char* const mine = scratch + (static_cast<long long>(w.piece) * CG + crank) * slot_bytes;
+        const int my_tile_row = quarter * 32 + lane;
+        for (int c = 0; c < bn; c += 32) {
+          uint32_t r0[32];
+          ptx::tmem_ld_32x32(t_base + c, r0);
+          ptx::tmem_ld_wait();
+#pragma unroll
+          for (int v = 0; v < 8; ++v)
+            ptx::st_global_v4(mine + split_vec_offset(c / 4 + v, my_tile_row),
+                              make_uint4(r0[4 * v], r0[4 * v + 1], r0[4 * v + 2], r0[4 * v + 3]));
+        }
+        ptx::tc_fence_before();
+        __threadfence();                                   // the partial is visible device-wide
+        asm volatile("bar.sync 1, 128;" ::: "memory");     // ... for all four epilogue warps
+        const int tail_tile = w.piece / split.parts, part = w.piece % split.parts;
+        uint32_t* const counter = p.split_counters + tail_tile * CG + crank;
+        if (warp == 4 && lane == 0) atomicAdd(counter, 1u);
+        // every piece of this tile half has arrived?
+        {
+          const uint32_t want = static_cast<uint32_t>(split.parts);
+          const bool ok = bounded_wait<true>(wc, [&] { return ptx::ld_acquire_gpu(counter) >= want; },
+                                             ST_TIMEOUT_PIPE, 0x700u, static_cast<uint32_t>(w.piece));
+          if (!__all_sync(0xffffffffu, ok)) break;
+        }
+        // Sum rows [part * R, part * R + R) of this CTA's 128 over all pieces, in piece order.
+        const int R = (kBlockM + split.parts - 1) / split.parts;
+        const int r_lo = part * R;
+        int r_hi = r_lo + R;
+        if (r_hi > ti.rows) r_hi = ti.rows;
+        const int nr = r_hi - r_lo;
+        if (nr > 0) {
+          const int n_cv = out_bn / 4;                     // output vectors (4 columns) per row
+          const char* const first = scratch + (static_cast<long long>(tail_tile) * split.parts * CG + crank) * slot_bytes;
+          const long long piece_stride = slot_bytes * CG;
+          const int tid = (warp - 4) * 32 + lane;
+          const int n0_out = glu ? ti.n0 / 2 : ti.n0;
+          for (int id = tid; id < n_cv * nr; id += 128) {
+            const int row = r_lo + id % nr, cv = id / nr;
+            const int col = n0_out + cv * 4;
+            if (col >= n_out) continue;
+            float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f, u0 = 0.f, u1 = 0.f, u2 = 0.f, u3 = 0.f;
+            const char* q = first + split_vec_offset(cv, row);
+            for (int pc = 0; pc < split.parts; ++pc, q += piece_stride) {
+              const float4 x = __ldcg(reinterpret_cast<const float4*>(q));
+              a0 += x.x; a1 += x.y; a2 += x.z; a3 += x.w;
+              if (glu) {
+                const float4 y = __ldcg(reinterpret_cast<const float4*>(q + split_vec_offset(n_cv, 0)));
+                u0 += y.x; u1 += y.y; u2 += y.z; u3 += y.w;
+              }
+            }
+            if (glu) {
+              a0 = __uint_as_float(silu_mul(__float_as_uint(a0), __float_as_uint(u0)));
+              a1 = __uint_as_float(silu_mul(__float_as_uint(a1), __float_as_uint(u1)));
+              a2 = __uint_as_float(silu_mul(__float_as_uint(a2), __float_as_uint(u2)));
+              a3 = __uint_as_float(silu_mul(__float_as_uint(a3), __float_as_uint(u3)));
+            }
+            uint2 o;
+            o.x = ptx::pack_bf16x2(a0, a1);
+            o.y = ptx::pack_bf16x2(a2, a3);
+            *reinterpret_cast<uint2*>(c_local + static_cast<long long>(ti.row0 + row) * ldc + col) = o;
+          }
+        }
+        __syncwarp();
+        if (lane == 0) {
+          if (CG == 1) ptx::mbar_arrive(tempty0 + 8u * acc);
+          else ptx::mbar_arrive_cluster(tempty0 + 8u * acc);
+        }
+        acc ^= 1;
+        if (acc == 0) acc_phase ^= 1u;
+        continue;
+      }
       if (OP == OP_RS && world > 1) {
         // Rows of this tile go into their owners' buffers: an owner's buffer may be written
         // only once that owner has entered this launch (its previous reduce has ended).

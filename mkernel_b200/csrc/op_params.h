@@ -45,6 +45,12 @@ struct OpParams {
   void* peer_out[kMaxWorld];
   void* mc_data;         // multicast alias of peer_data (or nullptr)
   void* mc_out;          // multicast alias of peer_out (or nullptr)
+  // Splitting the tiles of a partial last round along K (plain GEMM, AllGather+GEMM): fp32
+  // scratch for the pieces' accumulators (one 128 x block_n slot per CTA), arrival counters
+  // (zeroed by the host before the launch), and the largest number of pieces per tile (0 = off).
+  float* split_scratch;
+  uint32_t* split_counters;
+  int split_max_parts;
   // Diagnostics build only: 16 counters per CTA (cycles each role spent waiting); else nullptr.
   unsigned long long* trace;
 };

@@ -59,6 +59,9 @@ struct Options {
   // memory) overlaps the tail of the previous kernel in the stream; the reference launches the
   // same way (src/gemm_rs_blackwell.cu:668-680, src/ag_gemm_warp_specialized.cu:678-690).
   long long pdl = 1;
+  // 1: cut the tiles of a partial last round along K over all CTAs (plain GEMM and
+  // AllGather+GEMM); needs a per-stream scratch buffer the library allocates on first use.
+  long long split_tail = 1;
 };
 static Options g_opt;
 static std::mutex g_opt_mu;
@@ -73,6 +76,7 @@ static long long* option_slot(const char* name) {
   if (!strcmp(name, "use_nvls")) return &g_opt.use_nvls;
   if (!strcmp(name, "cta_pair")) return &g_opt.cta_pair;
   if (!strcmp(name, "pdl")) return &g_opt.pdl;
+  if (!strcmp(name, "split_tail")) return &g_opt.split_tail;
 #ifdef MKB_DIAG
   if (!strcmp(name, "debug_flags")) return &g_opt.debug_flags;
   if (!strcmp(name, "trace_ptr")) return &g_opt.trace_ptr;
@@ -391,6 +395,40 @@ static int launch_kernel(const Plan& pl, const CUtensorMap& ta, const CUtensorMa
   return MK_OK;
 }
 
+// ------------------------------------------------------------------------------------------
+// scratch for split tail tiles
+// ------------------------------------------------------------------------------------------
+// One buffer per (device, stream), allocated on first use and kept: launches on one stream are
+// serialised, so they can share it; launches on different streams may overlap and must not.
+// Layout: 4 KiB of arrival counters, then one 128 x 256 fp32 slot per SM.  The reference keeps
+// hidden per-device scratch the same way (include/operators/gemm_rs/gemm_rs.cuh:428-475).
+// Returns nullptr (splitting stays off for this launch) when the stream is being captured and
+// has no buffer yet, when the cache is full, or when the allocation fails.
+constexpr size_t kSplitCounterBytes = 4096;
+static char* split_scratch_for(cudaStream_t stream, int num_sms) {
+  struct Entry { int dev; cudaStream_t stream; char* ptr; };
+  static Entry cache[16];
+  static int n_cached = 0;
+  static std::mutex mu;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return nullptr;
+  std::lock_guard<std::mutex> g(mu);
+  for (int i = 0; i < n_cached; ++i)
+    if (cache[i].dev == dev && cache[i].stream == stream) return cache[i].ptr;
+  if (n_cached == 16) return nullptr;
+  cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(stream, &cap) != cudaSuccess || cap != cudaStreamCaptureStatusNone) {
+    cudaGetLastError();
+    return nullptr;
+  }
+  void* ptr = nullptr;
+  const size_t bytes = kSplitCounterBytes + (size_t)num_sms * kBlockM * 256 * 4;
+  if (cudaMalloc(&ptr, bytes) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+  if (cudaMemset(ptr, 0, kSplitCounterBytes) != cudaSuccess) { cudaGetLastError(); cudaFree(ptr); return nullptr; }
+  cache[n_cached++] = Entry{dev, stream, static_cast<char*>(ptr)};
+  return static_cast<char*>(ptr);
+}
+
 struct OpArgs {
   int op;
   const void* A;       // GEMM A operand (AG: local gathered buffer)
@@ -483,6 +521,23 @@ static int run_op(const OpArgs& a, cudaStream_t stream) {
   for (int r = 0; r < a.world; ++r) {
     if ((a.sync && !p.peer_sync[r]) || (a.data && !p.peer_data[r]) || (a.out && !p.peer_out[r]))
       return set_error(MK_ERR_INVALID, "symmetric view has no address for rank %d", r);
+  }
+
+  // Split tail tiles (plain GEMM, AllGather+GEMM): the kernel decides from its actual grid
+  // whether the last round is partial enough; here it only gets the scratch and clean counters.
+  if ((a.op == OP_GEMM || a.op == OP_AG) && o.split_tail != 0 && pl.n_comm == 0 &&
+      (long long)pl.sched.P * pl.sched.Q > pl.grid && pl.k_blocks >= 8) {
+    const int units = pl.grid / pl.cg;
+    const long long unit_tiles = (long long)pl.sched.P * pl.sched.Q / pl.cg;
+    const int rem = (int)(unit_tiles % units);
+    if (rem != 0 && rem <= units / 2) {
+      if (char* scratch = split_scratch_for(stream, sms)) {
+        MKB_CUDA(cudaMemsetAsync(scratch, 0, kSplitCounterBytes, stream));
+        p.split_counters = reinterpret_cast<uint32_t*>(scratch);
+        p.split_scratch = reinterpret_cast<float*>(scratch + kSplitCounterBytes);
+        p.split_max_parts = 32;
+      }
+    }
   }
 
   CUtensorMap ta, tb;

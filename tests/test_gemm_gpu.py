@@ -35,6 +35,10 @@ SHAPES = [
     (1024, 1024, 1024, NK, 0), (384, 640, 4096, NK, 128),
     (128, 64, 64, KN, 64), (128, 256, 128, KN, 256), (256, 512, 512, KN, 0),
     (200, 264, 136, KN, 0), (128, 8192, 1024, KN, 0), (77, 200, 328, KN, 192),
+    # a partial last round of tiles, cut along K over all CTAs (pair mode; single-CTA mode;
+    # ragged rows and columns in the cut tiles)
+    (1280, 4096, 2048, NK, 0), (1152, 4352, 1024, NK, 0), (1250, 4088, 2048, NK, 0),
+    (1280, 4096, 2048, KN, 0),
 ]
 
 
@@ -51,6 +55,22 @@ def test_gemm_is_deterministic():
     _, _, c1 = run_gemm(512, 768, 1024, NK)
     _, _, c2 = run_gemm(512, 768, 1024, NK)
     assert torch.equal(c1, c2)
+
+
+def test_split_last_round_is_deterministic_and_optional():
+    """The K-split of a partial last round sums its pieces in a fixed order: two runs agree bit
+    for bit; with the option off the whole tiles give the same result within rounding."""
+    _, _, c1 = run_gemm(1280, 4096, 2048, NK)
+    a, b_kn, c2 = run_gemm(1280, 4096, 2048, NK)
+    assert torch.equal(c1, c2)
+    _lib.set_option("split_tail", 0)
+    try:
+        _, _, c3 = run_gemm(1280, 4096, 2048, NK)
+    finally:
+        _lib.set_option("split_tail", 1)
+    _, ref = orc.ag_gemm_ref([a], b_kn)
+    assert orc.rel_error(c3, ref) <= orc.REL_TOL
+    assert (c1.float() - c3.float()).abs().max() <= 2 ** -6 * ref.abs().max()
 
 
 def test_gemm_exact_on_small_integers():

@@ -209,7 +209,12 @@ def test_swiglu_epilogue_and_mlp_chain_world1():
     chain's output within the tolerance of an oracle that also stores H as bf16."""
     from mkernel_b200 import ops
     torch.cuda.set_device(0)
-    M, K, I, N = 384, 320, 256, 264
+    _mlp_chain_world1(384, 320, 256, 264)
+    _mlp_chain_world1(1280, 2048, 2048, 512)     # the gate/up GEMM's last round is cut along K
+
+
+def _mlp_chain_world1(M, K, I, N):
+    from mkernel_b200 import ops
     g = torch.Generator().manual_seed(5)
     x = torch.randn((M, K), generator=g).to(torch.bfloat16)
     wg = (torch.randn((I, K), generator=g) / K ** 0.5).to(torch.bfloat16)
