@@ -761,8 +761,12 @@ def mlp_chain_record(dst, ops, peaks, steps):
               "rel_activation": dst.max_over_ranks(rel_h),
               "gathered_exact": bool(torch.equal(mlp.x.data_.view(M, K), x_full)),
               "tolerance": PARITY_TOL}
-    parity["ok"] = bool(parity["rel"] <= PARITY_TOL and parity["rel_activation"] <= PARITY_TOL and
-                        parity["gathered_exact"])
+    # Two bf16 roundings lie between the inputs and this output (H, then the partial products),
+    # and H is computed with the fast exponential: the chain is held to 1.5e-2, each of its two
+    # operators alone to 1e-2 (the activation here, GEMM+ReduceScatter in its own record).
+    parity["tolerance_chain"] = 1.5 * PARITY_TOL
+    parity["ok"] = bool(parity["rel"] <= parity["tolerance_chain"] and
+                        parity["rel_activation"] <= PARITY_TOL and parity["gathered_exact"])
     del part, ref, scale, h_ref, x_full
 
     # the same two operators, activation as its own kernel on [M, 2I]

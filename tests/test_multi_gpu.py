@@ -158,7 +158,8 @@ def test_tensor_parallel_mlp_chain():
         dict(op="mlp", M=world * 128, K=256, I=world * 256, N=512, seed=9, iters=3, max_rows=4096),
         dict(op="mlp", M=world * 256, K=1024, I=world * 128, N=264, seed=10, iters=2, max_rows=4096),
     ]
-    check(launch(world, cases), label="TP MLP chain")
+    # two bf16 roundings (H, then the partial products) lie between inputs and output
+    check(launch(world, cases), rel_tol=1.5 * orc.REL_TOL, label="TP MLP chain")
 
 
 @pytest.mark.skipif(n_gpus() < 2, reason="needs at least 2 GPUs")
