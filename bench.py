@@ -37,11 +37,11 @@ NVLINK_GBS = 900.0                           # per direction per GPU (nominal NV
 FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0)
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one fused launch at the headline shape on one
-# GPU.  Captured with ncu on the half-height case (M=4096: 287.8 MB read + 25.3 MB written per
-# launch, profiles/fused_gemm_kernel_ag_4096x3584x8192.md) and scaled by the tiles processed
-# (x2 for M=8192): the raster re-streams B once per group of row-blocks, so traffic grows with
-# the number of row-blocks.  Algorithmic bytes of the full launch: 251.7 MB.
-NCU_TRAFFIC_BYTES_PER_LAUNCH = 2 * (287.79e6 + 25.32e6)
+# GPU.  Captured with ncu on the half-height case (M=4096: 286.6 MB read + 24.2 MB written per
+# launch, profiles/fused_gemm_kernel_vs_cublas_4096x3584x8192.md) and scaled by the tiles
+# processed (x2 for M=8192): the raster re-streams B once per group of row-blocks, so traffic
+# grows with the number of row-blocks.  Algorithmic bytes of the full launch: 251.7 MB.
+NCU_TRAFFIC_BYTES_PER_LAUNCH = 2 * (286.62e6 + 24.25e6)
 
 
 def load_peaks():

@@ -509,10 +509,19 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
         }
         ptx::tc_fence_before();
         __threadfence();                                   // the partial is visible device-wide
-        asm volatile("bar.sync 1, 128;" ::: "memory");     // ... for all four epilogue warps
+        __syncwarp();
         const int tail_tile = w.piece / split.parts, part = w.piece % split.parts;
         uint32_t* const counter = p.split_counters + tail_tile * CG + crank;
-        if (warp == 4 && lane == 0) atomicAdd(counter, 1u);
+        // The CTA's arrival is announced once all four epilogue warps have stored their rows.
+        // They meet through a shared counter and a bounded wait, never through a hardware
+        // barrier: a warp that gave up on an earlier wait must not leave the others stuck.
+        if (lane == 0) atomicAdd(const_cast<uint32_t*>(s_progress) + 2, 1u);
+        if (warp == 4 && lane == 0) {
+          volatile uint32_t* stored = s_progress + 2;
+          if (bounded_wait<true>(wc, [&] { return *stored >= 4u; }, ST_TIMEOUT_PIPE, 0x701u,
+                                 static_cast<uint32_t>(w.piece)))
+            atomicAdd(counter, 1u);
+        }
         // every piece of this tile half has arrived?
         {
           const uint32_t want = static_cast<uint32_t>(split.parts);
@@ -1339,6 +1348,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
     *s_abort = 0u;
     *s_progress = 0u;
     *s_items_done = 0u;
+    s_words[5] = 0u;            // epilogue warps that have stored their rows of a tail piece
     if (!is_comm) {
       for (int i = 0; i < kMaxStages; ++i) {
         ptx::mbar_init(bar_base + 8u * (BAR_FULL + i), 1);
