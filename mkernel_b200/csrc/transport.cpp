@@ -94,11 +94,27 @@ struct mk_comm {
 
 namespace mkb {
 
+// Abstract-namespace address "mkb200/<key>/<rank>".  A key that would not fit (a fully
+// qualified host name plus a run id, say) is replaced by two 64-bit hashes of it, so that the
+// rank suffix is never cut off and two long keys sharing a prefix do not collide.
 static socklen_t make_addr(const std::string& key, int rank, sockaddr_un* a) {
   memset(a, 0, sizeof(*a));
   a->sun_family = AF_UNIX;
   char name[100];
-  int n = snprintf(name, sizeof(name), "mkb200/%s/%d", key.c_str(), rank);
+  int n;
+  if (key.size() <= 64) {
+    n = snprintf(name, sizeof(name), "mkb200/%s/%d", key.c_str(), rank);
+  } else {
+    uint64_t h1 = 1469598103934665603ull, h2 = 0x9E3779B97F4A7C15ull;
+    for (unsigned char ch : key) {
+      h1 = (h1 ^ ch) * 1099511628211ull;                    // FNV-1a
+      h2 = (h2 + ch) * 0xFF51AFD7ED558CCDull; h2 ^= h2 >> 33;
+    }
+    n = snprintf(name, sizeof(name), "mkb200/#%016llx%016llx.%zu/%d", (unsigned long long)h1,
+                 (unsigned long long)h2, key.size(), rank);
+  }
+  if (n < 0) n = 0;
+  if (n > (int)sizeof(name) - 1) n = sizeof(name) - 1;      // never read past `name`
   if (n > (int)sizeof(a->sun_path) - 2) n = sizeof(a->sun_path) - 2;
   a->sun_path[0] = '\0';  // abstract namespace
   memcpy(a->sun_path + 1, name, n);

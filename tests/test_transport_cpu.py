@@ -106,3 +106,21 @@ def test_two_ranks_cannot_claim_the_same_name():
     assert lib.mk_comm_create(key, 0, 2, 0, ctypes.byref(b)) == -3
     assert "bind" in _lib.last_error()
     lib.mk_comm_destroy(a)
+
+
+def test_long_keys_keep_their_rank_suffix():
+    """A rendezvous key longer than a socket name (a fully qualified host name plus a run id)
+    must neither cut off the rank suffix nor collide with another long key sharing a prefix."""
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    prefix = "node-0123.some-cluster.example.internal:29500:" + "x" * 90
+    jobs = []
+    for tag in ("a", "b"):                      # two jobs whose keys differ only at the very end
+        key = prefix + tag
+        jobs += [ctx.Process(target=_rank_main, args=(r, 2, key, q, 1)) for r in range(2)]
+    for p in jobs:
+        p.start()
+    got = [q.get(timeout=120) for _ in range(4)]
+    for p in jobs:
+        p.join(30)
+    assert all(status == "ok" for _, status, _ in got), got
