@@ -166,6 +166,29 @@ def timed_loop(dst: Dist, step, steps: int, warmup: int, sampler=None):
     return total, kern
 
 
+def interleaved_ms(dst: Dist, step_a, step_b, rounds: int, per_round: int):
+    """Mean fused-launch time of two arms timed in alternating blocks (a, b, a, b, ...), so that
+    both see the same power and thermal state: on this power-capped part a seconds-long kernel
+    sequence timed after another one runs measurably slower than the same sequence timed first.
+    Returns (ms_a, ms_b), each the max over ranks of the mean over all its blocks."""
+    null = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+    for i in range(3):
+        step_a(i, *null)
+        step_b(i, *null)
+    sums = [0.0, 0.0]
+    for r in range(rounds):
+        for arm, step in enumerate((step_a, step_b)):
+            evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+                   for _ in range(per_round)]
+            dst.barrier()
+            for i, (e0, e1) in enumerate(evs):
+                step(3 + r * per_round + i, e0, e1)
+            torch.cuda.synchronize()
+            sums[arm] += sum(a.elapsed_time(b) for a, b in evs)
+    n = rounds * per_round
+    return dst.max_over_ranks(sums[0] / n), dst.max_over_ranks(sums[1] / n)
+
+
 def graph_time_us(dst: Dist, fn, launches: int, replays: int) -> float:
     """Mean microseconds per call of fn when `launches` calls are captured in one CUDA graph and
     the graph is replayed `replays` times (max over ranks)."""
@@ -468,8 +491,10 @@ def run_ours(args):
         e1.record()
 
     sub_steps = max(5, min(steps, 20))
-    _, ag_unf_ms = timed_loop(dst, ag_unfused, sub_steps, 3)
-    ops_out["ag_gemm"] = op_record("AllGather+GEMM", CFG2, W, kern_ms, ag_unf_ms, flops_per_gpu,
+    # fused and unfused arms of every operator record are timed in alternating blocks
+    ag_f_ms, ag_unf_ms = interleaved_ms(dst, ag_step, ag_unfused, 4, max(2, sub_steps // 4))
+    ag.op_status(ready)
+    ops_out["ag_gemm"] = op_record("AllGather+GEMM", CFG2, W, ag_f_ms, ag_unf_ms, flops_per_gpu,
                                    ag_bytes, peaks)
     ops_out["ag_gemm"]["parity"] = ag_parity
     ops_out["ag_gemm"]["nvlink_measured"] = ag_nvlink
@@ -492,8 +517,6 @@ def run_ours(args):
         rs.gemm_rs_blackwell_launch(A3, B3, C3, sync3)
         e1.record()
 
-    _, rs_ms = timed_loop(dst, rs_step, sub_steps, 3)
-    rs.op_status(sync3)
     rs_nvlink = nvl.per_launch(lambda i: rs_step(i, *null_ev), 50, sync) if nvl else None
     c3 = torch.empty((M3, N3), device=dev, dtype=torch.bfloat16)
     c3_rs = torch.empty((M3 // W, N3), device=dev, dtype=torch.bfloat16)
@@ -505,7 +528,8 @@ def run_ours(args):
             dst.dist.reduce_scatter_tensor(c3_rs, c3)
         e1.record()
 
-    _, rs_unf_ms = timed_loop(dst, rs_unfused, sub_steps, 3)
+    rs_ms, rs_unf_ms = interleaved_ms(dst, rs_step, rs_unfused, 4, max(2, sub_steps // 4))
+    rs.op_status(sync3)
     ops_out["gemm_rs"] = op_record("GEMM+ReduceScatter", CFG3, W, rs_ms, rs_unf_ms,
                                    2.0 * M3 * N3 * K3, (W - 1) / W * M3 * N3 * 2, peaks)
     del c3, c3_rs
@@ -741,7 +765,8 @@ def mlp_chain_record(dst, ops, peaks, steps):
         mlp.forward()
         e1.record()
 
-    _, fused_ms = timed_loop(dst, fused, steps, 3)
+    for i in range(3):
+        fused(i, torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
     ops.op_status(mlp.ready); ops.op_status(mlp.sync)
     # parity of the chain (untimed): fp32 products of the same bf16 operands, H stored as bf16
     y = mlp.forward()
@@ -781,7 +806,7 @@ def mlp_chain_record(dst, ops, peaks, steps):
         ops.gemm_rs_blackwell_launch(mlp.h.view(M, I), mlp.w_down, mlp.y, mlp.sync)
         e1.record()
 
-    _, sep_ms = timed_loop(dst, separate, steps, 3)
+    fused_ms, sep_ms = interleaved_ms(dst, fused, separate, 4, max(2, steps // 4))
     ops.op_status(mlp.ready); ops.op_status(mlp.sync)
     del gu
     # unfused: NCCL all-gather, cuBLAS, elementwise, cuBLAS, NCCL reduce-scatter
@@ -805,14 +830,15 @@ def mlp_chain_record(dst, ops, peaks, steps):
             dst.dist.reduce_scatter_tensor(y_rs, yy)
         e1.record()
 
-    _, unf_ms = timed_loop(dst, unfused, steps, 3)
+    fused_vs_sep_ms = fused_ms
+    fused_ms, unf_ms = interleaved_ms(dst, fused, unfused, 4, max(2, steps // 4))
     flops = 2.0 * M * (2 * I) * K + 2.0 * M * N * I
     nvlink = (W - 1) / W * (M * K + M * N) * 2
     t_roof = max(flops / (peaks["bf16_tflops"] * 1e12), nvlink / (NVLINK_GBS * 1e9)) * 1e3
     rec = {"name": "TP MLP chain (AG+GEMM gate/up + SwiGLU -> GEMM+RS down)",
            "shape": {"M": M, "K": K, "I_per_gpu": I, "N": N}, "tp": W,
            "fused_ms": fused_ms, "separate_activation_ms": sep_ms, "unfused_ms": unf_ms,
-           "speedup_vs_separate": sep_ms / fused_ms, "speedup_vs_unfused": unf_ms / fused_ms,
+           "speedup_vs_separate": sep_ms / fused_vs_sep_ms, "speedup_vs_unfused": unf_ms / fused_ms,
            "tflops_per_gpu": flops / (fused_ms * 1e-3) / 1e12,
            "fused_roofline_ms": t_roof, "fused_roofline_frac": t_roof / fused_ms,
            "launches_per_step": 2, "parity": parity}
@@ -832,7 +858,8 @@ def headline_config(W):
 def run_sweep(args):
     """The scaling sweep: AllGather+GEMM and GEMM+ReduceScatter at total M in {2048, 8192, 32768},
     K = 8192, global N = 28672 sharded by the world size.  Prints one JSON line {"sweep": [...]}
-    with TFLOP/s per GPU, the fused-roofline fraction and the unfused cuBLAS(+NCCL) time."""
+    with TFLOP/s per GPU, the fused-roofline fraction and the unfused cuBLAS(+NCCL) time.  The two
+    arms of a point are timed in alternating blocks (see interleaved_ms)."""
     import mkernel_b200
 
     dst = Dist(args.gpus)
@@ -874,9 +901,8 @@ def run_sweep(args):
                 torch.matmul(A.data_[rank], B.t(), out=C2)
             e1.record()
 
-        _, f_ms = timed_loop(dst, ag_step, steps, 3)
+        f_ms, u_ms = interleaved_ms(dst, ag_step, ag_unf, 4, max(2, steps // 4))
         ag.op_status(ready)
-        _, u_ms = timed_loop(dst, ag_unf, steps, 3)
         out.append(op_record("AllGather+GEMM", dict(M=M, N=Nl, K=K), W, f_ms, u_ms,
                              2.0 * M * Nl * K, (W - 1) / W * M * K * 2, peaks))
         A.free(); ready.free()
@@ -905,9 +931,8 @@ def run_sweep(args):
                 dst.dist.reduce_scatter_tensor(c3r, c3)
             e1.record()
 
-        _, f_ms = timed_loop(dst, rs_step, steps, 3)
+        f_ms, u_ms = interleaved_ms(dst, rs_step, rs_unf, 4, max(2, steps // 4))
         rs.op_status(s3)
-        _, u_ms = timed_loop(dst, rs_unf, steps, 3)
         out.append(op_record("GEMM+ReduceScatter", dict(M=M, N=N3, K=Kl), W, f_ms, u_ms,
                              2.0 * M * N3 * Kl, (W - 1) / W * M * N3 * 2, peaks))
         C3.free(); s3.free()
