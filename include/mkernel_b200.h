@@ -217,6 +217,11 @@ int mk_plan_op(int op, int rank, int world, int M, int N, int K, int b_layout, i
  * (or a negative status).  `cap` is the capacity of each output array. */
 int mk_sched_tiles(int op, int rank, int world, int M, int N, int block_n, int group_rows,
                    int group_cols, int* row0, int* rows, int* col0, int* rowblock, int cap);
+/* Work list of compute CTA `cta` (of n_comp; cg = 2: CTAs work as pairs on consecutive tiles):
+ * whole tiles, then at most one piece [kb0, kb1) of a tile of a partial last round when
+ * splitting applies (max_parts >= 2; piece = -1 for whole tiles).  Returns the item count. */
+int mk_sched_work_items(int total_tiles, int n_comp, int cg, int k_blocks, int max_parts, int cta,
+                        int* tile, int* kb0, int* kb1, int* piece, int cap);
 /* Rows [row0,row1) that owner `owner` reduces for its k-th item; returns number of items. */
 int mk_sched_owner_items(int op, int world, int M, int N, int block_n, int owner, int* row0,
                          int* row1, int cap);

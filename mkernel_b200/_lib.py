@@ -106,6 +106,8 @@ _SIGNATURES = {
                            POINTER(Plan)]),
     "mk_sched_tiles": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, POINTER(c_int),
                                POINTER(c_int), POINTER(c_int), POINTER(c_int), c_int]),
+    "mk_sched_work_items": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, POINTER(c_int),
+                                    POINTER(c_int), POINTER(c_int), POINTER(c_int), c_int]),
     "mk_sched_owner_items": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, POINTER(c_int),
                                      POINTER(c_int), c_int]),
 }
@@ -169,3 +171,12 @@ def sched_owner_items(op: int, world: int, M: int, N: int, block_n: int, owner: 
     a, b = (c_int * max(n, 1))(), (c_int * max(n, 1))()
     check(lib().mk_sched_owner_items(op, world, M, N, block_n, owner, a, b, n))
     return [(a[i], b[i]) for i in range(n)]
+
+
+def sched_work_items(total_tiles: int, n_comp: int, cg: int, k_blocks: int, max_parts: int, cta: int):
+    """[(tile, kb0, kb1, piece)] of one compute CTA, in order."""
+    n = check(lib().mk_sched_work_items(total_tiles, n_comp, cg, k_blocks, max_parts, cta, None,
+                                        None, None, None, 0))
+    arr = [(c_int * max(n, 1))() for _ in range(4)]
+    check(lib().mk_sched_work_items(total_tiles, n_comp, cg, k_blocks, max_parts, cta, *arr, n))
+    return [tuple(a[i] for a in arr) for i in range(n)]

@@ -142,59 +142,17 @@ __device__ __forceinline__ void stamp_max(const OpParams& p, int slot) {
     atomicMax(p.sync + 24 + slot, static_cast<uint32_t>(global_timer_ns()));
 }
 
-// ------------------------------------------------------------------------------------------
-// Work of one compute CTA: whole tiles, then at most one piece of a tail tile.
-// ------------------------------------------------------------------------------------------
-// Tiles are handed out round-robin (tile t to CTA t mod n_comp), so the last round is usually
-// partial: with 6.05 rounds of tiles the 7th keeps 5 % of the CTAs busy for a whole tile time.
-// When splitting is enabled (plain GEMM and AllGather+GEMM), the tiles of a partial last round
-// are instead cut along K into `parts` pieces, one per CTA (CTA pair), so that every CTA gets a
-// share of that round; the pieces' fp32 accumulators go through a scratch buffer and are summed
-// in a fixed order (deterministic), each CTA finishing a slice of rows of its tile.
-struct SplitPlan {
-  int full_rounds;   // rounds in which every CTA has a whole tile
-  int rem_units;     // tail tiles (pair tiles for CG = 2) = units of the partial round
-  int parts;         // pieces per tail tile; 0 = no splitting (the partial round runs whole tiles)
-};
+// The split plan and the per-CTA work list live in sched.h (host + device, unit-tested on the
+// host); these wrappers bind them to the kernel's parameter block.
 template <int CG>
 __device__ __forceinline__ SplitPlan make_split(const OpParams& p, int total_tiles, int n_comp) {
-  SplitPlan sp;
-  sp.full_rounds = 0; sp.rem_units = 0; sp.parts = 0;
-  if (p.split_max_parts < 2 || p.split_scratch == nullptr) return sp;
-  const int units = n_comp / CG, unit_tiles = total_tiles / CG;
-  const int full = unit_tiles / units, rem = unit_tiles % units;
-  if (full < 1 || rem == 0 || rem > units / 2) return sp;
-  int parts = units / rem;
-  if (parts > p.split_max_parts) parts = p.split_max_parts;
-  if (parts > p.k_blocks / 4) parts = p.k_blocks / 4;
-  if (parts < 2) return sp;
-  sp.full_rounds = full; sp.rem_units = rem; sp.parts = parts;
-  return sp;
+  if (p.split_scratch == nullptr) return plan_split(total_tiles, n_comp, CG, p.k_blocks, 0);
+  return plan_split(total_tiles, n_comp, CG, p.k_blocks, p.split_max_parts);
 }
-struct WorkItem {
-  int t;          // tile index in visiting order
-  int kb0, kb1;   // k-blocks [kb0, kb1)
-  int piece;      // -1: the whole tile; else tail tile * parts + part
-};
-// `cta` = index of this CTA among the compute CTAs, `it` = 0, 1, 2, ... ; false when done.
 template <int CG>
 __device__ __forceinline__ bool work_item(const OpParams& p, const SplitPlan& sp, int total_tiles,
                                           int n_comp, int cta, int it, WorkItem& w) {
-  w.kb0 = 0; w.kb1 = p.k_blocks; w.piece = -1;
-  if (sp.parts == 0) {
-    w.t = cta + it * n_comp;
-    return w.t < total_tiles;
-  }
-  if (it < sp.full_rounds) { w.t = cta + it * n_comp; return true; }
-  if (it > sp.full_rounds) return false;
-  const int unit = cta / CG;
-  if (unit >= sp.rem_units * sp.parts) return false;
-  const int j = unit / sp.parts, i = unit % sp.parts;
-  w.t = sp.full_rounds * n_comp + j * CG + (cta % CG);
-  w.kb0 = static_cast<int>(static_cast<long long>(i) * p.k_blocks / sp.parts);
-  w.kb1 = static_cast<int>(static_cast<long long>(i + 1) * p.k_blocks / sp.parts);
-  w.piece = unit;
-  return true;
+  return cta_work_item(sp, total_tiles, n_comp, CG, p.k_blocks, cta, it, &w);
 }
 // Scratch layout of one piece of one CTA (128 rows x block_n fp32): 16-byte vectors in the order
 // [32-column chunk][vector of the chunk (8)][row (128)], so that the epilogue's stores (thread =

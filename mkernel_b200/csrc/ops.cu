@@ -864,6 +864,26 @@ int mk_sched_tiles(int op, int rank, int world, int M, int N, int block_n, int g
   return total;
 }
 
+int mk_sched_work_items(int total_tiles, int n_comp, int cg, int k_blocks, int max_parts, int cta,
+                        int* tile, int* kb0, int* kb1, int* piece, int cap) {
+  if (total_tiles < 1 || n_comp < 1 || (cg != 1 && cg != 2) || n_comp % cg != 0 ||
+      total_tiles % cg != 0 || k_blocks < 1 || cta < 0 || cta >= n_comp)
+    return set_error(MK_ERR_INVALID, "mk_sched_work_items: bad arguments");
+  const SplitPlan sp = plan_split(total_tiles, n_comp, cg, k_blocks, max_parts);
+  int n = 0;
+  WorkItem w;
+  for (int it = 0; cta_work_item(sp, total_tiles, n_comp, cg, k_blocks, cta, it, &w); ++it) {
+    if (n < cap) {
+      if (tile) tile[n] = w.t;
+      if (kb0) kb0[n] = w.kb0;
+      if (kb1) kb1[n] = w.kb1;
+      if (piece) piece[n] = w.piece;
+    }
+    ++n;
+  }
+  return n;
+}
+
 int mk_sched_owner_items(int op, int world, int M, int N, int block_n, int owner, int* row0,
                          int* row1, int cap) {
   if (world < 1 || world > kMaxWorld || owner < 0 || owner >= world || M < 1 || N < 1 ||

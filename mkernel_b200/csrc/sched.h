@@ -247,6 +247,60 @@ MKB_HD int choose_item_vecs(const Sched& s, int workers, int min_vecs = 128) {
   return (int)((v + 31) / 32 * 32);
 }
 
+// ------------------------------------------------------------------------------------------
+// Work of one compute CTA: whole tiles, then at most one piece of a tail tile.
+// ------------------------------------------------------------------------------------------
+// Tiles are handed out round-robin (tile t to CTA t mod n_comp), so the last round is usually
+// partial: with 6.05 rounds of tiles the 7th keeps 5 % of the CTAs busy for a whole tile time.
+// When splitting is enabled (plain GEMM and AllGather+GEMM), the tiles of a partial last round
+// are instead cut along K into `parts` pieces, one per CTA (CTA pair), so that every CTA gets a
+// share of that round; the pieces' fp32 accumulators go through a scratch buffer and are summed
+// in a fixed order (deterministic), each CTA finishing a slice of rows of its tile.
+// cg = 1: a unit is a CTA and a tile; cg = 2: a unit is a CTA pair and two consecutive tiles.
+struct SplitPlan {
+  int full_rounds;   // rounds in which every CTA has a whole tile
+  int rem_units;     // tail tiles (pair tiles for cg = 2) = units of the partial round
+  int parts;         // pieces per tail tile; 0 = no splitting (the partial round runs whole tiles)
+};
+MKB_HD SplitPlan plan_split(int total_tiles, int n_comp, int cg, int k_blocks, int max_parts) {
+  SplitPlan sp;
+  sp.full_rounds = 0; sp.rem_units = 0; sp.parts = 0;
+  if (max_parts < 2 || n_comp < cg) return sp;
+  const int units = n_comp / cg, unit_tiles = total_tiles / cg;
+  const int full = unit_tiles / units, rem = unit_tiles % units;
+  if (full < 1 || rem == 0 || rem > units / 2) return sp;
+  int parts = units / rem;
+  if (parts > max_parts) parts = max_parts;
+  if (parts > k_blocks / 4) parts = k_blocks / 4;   // at least four k-blocks per piece
+  if (parts < 2) return sp;
+  sp.full_rounds = full; sp.rem_units = rem; sp.parts = parts;
+  return sp;
+}
+struct WorkItem {
+  int t;          // tile index in visiting order
+  int kb0, kb1;   // k-blocks [kb0, kb1)
+  int piece;      // -1: the whole tile; else tail tile * parts + part
+};
+// `cta` = index of this CTA among the compute CTAs, `it` = 0, 1, 2, ... ; false when done.
+MKB_HD bool cta_work_item(const SplitPlan& sp, int total_tiles, int n_comp, int cg, int k_blocks,
+                          int cta, int it, WorkItem* w) {
+  w->kb0 = 0; w->kb1 = k_blocks; w->piece = -1;
+  if (sp.parts == 0) {
+    w->t = cta + it * n_comp;
+    return w->t < total_tiles;
+  }
+  if (it < sp.full_rounds) { w->t = cta + it * n_comp; return true; }
+  if (it > sp.full_rounds) return false;
+  const int unit = cta / cg;
+  if (unit >= sp.rem_units * sp.parts) return false;
+  const int j = unit / sp.parts, i = unit % sp.parts;
+  w->t = sp.full_rounds * n_comp + j * cg + (cta % cg);
+  w->kb0 = (int)((long long)i * k_blocks / sp.parts);
+  w->kb1 = (int)((long long)(i + 1) * k_blocks / sp.parts);
+  w->piece = unit;
+  return true;
+}
+
 // Shared-memory plan for one CTA.
 MKB_HD int stage_bytes(int block_n) { return kBlockM * kBlockK * 2 + block_n * kBlockK * 2; }
 // Same for a CTA pair (cg = 2): each CTA holds its A tile and half of the B tile.

@@ -137,3 +137,42 @@ def test_two_level_raster_covers_every_tile_once_and_keeps_pairs_in_one_column(M
     a = _lib.sched_tiles(OP_AG, 1, 4, 8192, 3584, 256, 8, 4)
     b = _lib.sched_tiles(OP_AG, 1, 4, 8192, 3584, 256, 8, 0)
     assert a == b
+
+
+@pytest.mark.parametrize("total_tiles,n_comp,cg,k_blocks", [
+    (896, 148, 2, 128),     # the up-projection shape: 6.05 rounds, 4 tail pair-tiles cut in 18
+    (160, 148, 2, 32),      # 6 tail pair-tiles, pieces capped by four k-blocks each
+    (153, 148, 1, 16),      # single-CTA mode
+    (224, 148, 2, 128),     # more than half a round left: no cut
+    (296, 148, 2, 64),      # exact rounds: no cut
+    (100, 148, 1, 64),      # less than one round: no cut
+    (300, 146, 2, 9),       # a grid capped below the SM count, few k-blocks
+])
+def test_work_lists_cover_every_tile_and_k_block_once(total_tiles, n_comp, cg, k_blocks):
+    """Whole tiles plus the pieces of a cut last round: every (tile, k-block) exactly once, the
+    two CTAs of a pair on consecutive tiles with the same k-range, pieces of a tile in order."""
+    seen = {}
+    pieces = {}
+    for cta in range(n_comp):
+        for tile, kb0, kb1, piece in _lib.sched_work_items(total_tiles, n_comp, cg, k_blocks, 32, cta):
+            assert 0 <= tile < total_tiles and 0 <= kb0 < kb1 <= k_blocks
+            for kb in range(kb0, kb1):
+                assert (tile, kb) not in seen, (tile, kb, cta, seen[(tile, kb)])
+                seen[(tile, kb)] = cta
+            if piece >= 0:
+                assert kb1 - kb0 >= 4
+                pieces.setdefault(tile, []).append((piece, kb0, kb1, cta))
+            else:
+                assert (kb0, kb1) == (0, k_blocks)
+            if cg == 2:
+                assert tile % 2 == cta % 2          # pair member c takes tile 2m + c
+    assert len(seen) == total_tiles * k_blocks
+    for tile, lst in pieces.items():
+        lst.sort()
+        assert lst[0][1] == 0 and lst[-1][2] == k_blocks
+        assert all(a[2] == b[1] for a, b in zip(lst, lst[1:]))      # contiguous, in piece order
+        assert len(lst) >= 2
+    # no cut requested: plain round-robin
+    plain = [_lib.sched_work_items(total_tiles, n_comp, cg, k_blocks, 0, c) for c in range(n_comp)]
+    assert sorted(t for items in plain for t, _, _, _ in items) == list(range(total_tiles))
+    assert all(p == -1 for items in plain for _, _, _, p in items)
