@@ -372,6 +372,13 @@ def run_ours(args):
         ag.ag_gemm_warp_specialized_launch(A, ready, B, C)
         e1.record()
 
+    # Set-up, untimed: an idle GPU sits at its lowest clocks and takes tens of milliseconds of
+    # work to ramp; without this the first timed steps of a short run measure the ramp (at four
+    # GPUs one slow-ramping rank held the whole job at 0.62 of peak instead of 0.75).
+    ramp_ev = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+    for i in range(60):
+        ag_step(i, *ramp_ev)
+    dst.barrier()
     sampler = ClockSampler(rank)
     total_ms, kern_ms = timed_loop(dst, ag_step, steps, warmup, sampler)
     ag.op_status(ready)
