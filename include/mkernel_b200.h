@@ -184,7 +184,9 @@ int mk_op_status_clear(const mk_symm_view* sync, void* stream);
  *      "ar_one_shot" (GEMM+AR: 0 = two-shot, owners reduce and broadcast; 1 = one-shot, every
  *      rank reduces all rows for itself), "ag_fanout" (AllGather push: 0 = one work item per
  *      receiver, 1 = an item loads its rows once and stores them to every peer), "push_bulk"
- *      (AllGather push through bulk shared-to-global stores), "ag_lead" (AllGather push pacing:
+ *      (AllGather push through bulk shared-to-global stores), "ag_chunks" (AllGather push: 0 =
+ *      an item is 4 full rows and consumers wait for whole row-blocks; 1 = an item is every row
+ *      of a row-block over one K-range and consumers wait range by range inside the K loop), "ag_lead" (AllGather push pacing:
  *      rows are pushed at most this many quarter raster groups before the GEMM reaches the group
  *      that consumes them; default 6, 0 = push as fast as possible), "pdl" (0/1, default 1: launch with
  *      programmatic stream serialization so a kernel's set-up overlaps the previous kernel's

@@ -247,6 +247,9 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
     const uint32_t full0_local = bar(BAR_FULL), empty0 = bar(BAR_EMPTY);
     const uint32_t tx_bytes = static_cast<uint32_t>(CG * stage_sz);
     const int b_panels = b_rows / 64;
+    // AllGather in K-range form: vectors per range (log2) and ranges per row
+    const int ag_lg = OP == OP_AG ? p.ag_cv_log2 : 0;
+    const int ag_ranges = ag_lg != 0 ? ((p.K / 8) + (1 << ag_lg) - 1) >> ag_lg : 0;
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
@@ -256,15 +259,24 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
       const int t = w.t;
       const TileInfo ti = tile_info(s, t);
       if (OP == OP_AG && lane == 0) *s_progress = static_cast<uint32_t>(t);
+      uint32_t landed = 0xffffffffu;   // K-ranges of this tile's rows known to have landed here
+      const uint32_t* range_flags = nullptr;
       if (OP == OP_AG && s.world > 1 && rowblock_shard(s, ti.rowblock) != s.rank) {
-        // Rows of a remote shard: wait until the sender has landed all 4-row groups here.
-        static_assert(kGatherSub == 32, "one group flag per producer lane");
+        static_assert(kGatherSub == 32, "one group / range flag per producer lane");
         const uint32_t* f = p.sync + SW_FLAGS + gather_flag_index(ti.rowblock, lane);
         const long long c0 = diag_clock(tr);
-        const bool mine = bounded_wait<true>(wc, [&] { return ptx::ld_acquire_sys(f) == epoch; },
-                                             ST_TIMEOUT_GATHER, ti.rowblock, lane);
+        if (ag_lg == 0) {
+          // Rows of a remote shard: wait until the sender has landed all 4-row groups here.
+          const bool mine = bounded_wait<true>(wc, [&] { return ptx::ld_acquire_sys(f) == epoch; },
+                                               ST_TIMEOUT_GATHER, ti.rowblock, lane);
+          ok = __all_sync(0xffffffffu, mine);
+        } else {
+          // K-range form: note which ranges are here already; the K loop waits for the others
+          // one by one as it reaches them.
+          range_flags = f - lane;
+          landed = __ballot_sync(0xffffffffu, lane >= ag_ranges || ptx::ld_acquire_sys(f) == epoch);
+        }
         tr_gather += diag_clock(tr) - c0;
-        ok = __all_sync(0xffffffffu, mine);
         ptx::fence_proxy_async();  // rows stored by a peer GPU are about to be read by TMA
         if (!ok) break;
       }
@@ -273,6 +285,18 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
         const int nb0 = ti.n0 + crank * b_rows;   // first B row (C column) this CTA loads
         int kx = w.kb0 * kBlockK;                  // element offset of the k-block
         for (int kb = w.kb0; kb < w.kb1; ++kb, kx += kBlockK) {
+          if (OP == OP_AG && landed != 0xffffffffu) {
+            const int c = kb >> (ag_lg - 3);
+            if (((landed >> c) & 1u) == 0u) {
+              const uint32_t* f = range_flags + c;
+              const long long g0 = diag_clock(tr);
+              if (!bounded_wait<true>(wc, [&] { return ptx::ld_acquire_sys(f) == epoch; },
+                                      ST_TIMEOUT_GATHER, ti.rowblock, c)) { ok = false; break; }
+              tr_gather += diag_clock(tr) - g0;
+              ptx::fence_proxy_async();
+              landed |= 1u << c;
+            }
+          }
           const long long c0 = diag_clock(tr);
           if (!wait_mbar(wc, empty0 + 8u * stage, phase ^ 1u, 0x100u + stage)) { ok = false; break; }
           tr_empty += diag_clock(tr) - c0;
@@ -786,6 +810,63 @@ __device__ __forceinline__ void push_span(const char* src, char* const (&dst_in)
   ptx::cp_async_wait<0>();
 }
 
+// AllGather item in K-range form: `rows` rows of one row-block, each row's `valid_cv` (<= 2^lg_cv)
+// 16-byte vectors starting at the same column, from the own shard to the same offsets of one
+// destination.  Vector v of the item is (row v >> lg_cv, column v & (2^lg_cv - 1)); a warp step
+// therefore covers whole 128..512-byte row segments.  Same ring discipline as push_span.
+template <int R>
+__device__ __forceinline__ void push_chunk(const char* src, char* dst, int rows, long long row_bytes,
+                                           int lg_cv, int valid_cv, uint32_t ring, int lane) {
+  using G = PushRing<R>;
+  const int col_mask = (1 << lg_cv) - 1;
+  const int n_vec = rows << lg_cv;
+  const int n_mine = n_vec > lane ? (n_vec - 1 - lane) / 32 + 1 : 0;
+  const int n_steps = (n_mine + G::VP - 1) / G::VP;
+  const uint32_t ring_lane = ring + lane * 16u;
+  // byte offset of this lane's e-th vector, or -1 where the row has no such column
+  auto offset_of = [=](int e) -> long long {
+    const int v = e * 32 + lane;
+    const int col = v & col_mask;
+    if (e >= n_mine || col >= valid_cv) return -1;
+    return static_cast<long long>(v >> lg_cv) * row_bytes + col * 16;
+  };
+  int ld_step = 0, ld_slot = 0;
+  auto issue = [&]() {
+    if (ld_step < n_steps) {
+      const uint32_t sb = ring_lane + static_cast<uint32_t>(ld_slot) * G::kStepBytes;
+#pragma unroll
+      for (int j = 0; j < G::VP; ++j) {
+        const long long off = offset_of(ld_step * G::VP + j);
+        if (off >= 0) ptx::cp_async_16(sb + j * 512, src + off);
+      }
+    }
+    ptx::cp_async_commit();
+    ++ld_step;
+    if (++ld_slot == G::NS) ld_slot = 0;
+  };
+#pragma unroll 1
+  for (int i = 0; i < G::NS - 1; ++i) issue();
+  int slot = 0;
+#pragma unroll 1
+  for (int st = 0; st < n_steps; ++st) {
+    issue();
+    ptx::cp_async_wait<G::NS - 1>();
+    const uint32_t sb = ring_lane + static_cast<uint32_t>(slot) * G::kStepBytes;
+    uint4 v[G::VP];
+    long long off[G::VP];
+#pragma unroll
+    for (int j = 0; j < G::VP; ++j) {
+      off[j] = offset_of(st * G::VP + j);
+      v[j] = ptx::ld_shared_v4(sb + j * 512);
+    }
+#pragma unroll
+    for (int j = 0; j < G::VP; ++j)
+      if (off[j] >= 0) ptx::st_global_v4(dst + off[j], v[j]);
+    if (++slot == G::NS) slot = 0;
+  }
+  ptx::cp_async_wait<0>();
+}
+
 // Same copy to one destination, but every step (VP x 32 vectors = one contiguous range in both
 // the ring and the destination) leaves as ONE bulk store issued by lane 0: fewer, larger write
 // requests on NVLink.
@@ -1060,10 +1141,15 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
     if (OP == OP_AG) {
       // Item order: row-block j of the own shard goes to every receiver (nearest ring distance
       // first) before row-block j+1 goes to anybody -- the order in which receivers consume.
+      // K-range form (ag_cv_log2 != 0): range g of row-block j goes to every receiver before
+      // range g + 1 goes to anybody, so all receivers can start on the row-block early.
+      const int lg_cv = p.ag_cv_log2;
       const int per_block = (bcast_ag ? 1 : W - 1) * kGatherSub;
       const int j = item / per_block;
-      const int d = bcast_ag ? 0 : 1 + (item % per_block) / kGatherSub;   // receiver's ring distance
-      const int g = item % kGatherSub;
+      const int in_block = item % per_block;
+      // receiver's ring distance, and the 4-row group or K-range
+      const int d = bcast_ag ? 0 : 1 + (lg_cv != 0 ? in_block % (W - 1) : in_block / kGatherSub);
+      const int g = lg_cv != 0 ? in_block / (W - 1) : in_block % kGatherSub;
       const int rowblock = s.rank * s.part_blocks + j;
       const int rows_in_block = rowblock_rows(s, rowblock);
       const int r0 = g * (kBlockM / kGatherSub);
@@ -1100,7 +1186,17 @@ __device__ __forceinline__ void exchange_worker(const OpParams& p, uint32_t ring
           if (!__all_sync(0xffffffffu, ok)) return;
         }
       }
-      if (!diag(p, 1)) {
+      if (lg_cv != 0) {
+        const int first_vec = g << lg_cv;
+        const int row_vecs = static_cast<int>(row_bytes / 16);
+        int valid_cv = row_vecs - first_vec;
+        if (valid_cv > (1 << lg_cv)) valid_cv = 1 << lg_cv;
+        const long long cbase = static_cast<long long>(rowblock_row0(s, rowblock)) * row_bytes +
+                                static_cast<long long>(first_vec) * 16;
+        if (!diag(p, 1) && valid_cv > 0 && rows_in_block > 0)
+          push_chunk<R>(local + cbase, dst + cbase, rows_in_block, row_bytes, lg_cv, valid_cv, ring,
+                        lane);
+      } else if (!diag(p, 1)) {
         if (bcast_ag && !nvls_ag) {
           char* fan[kMaxWorld - 1];
 #pragma unroll

@@ -26,6 +26,9 @@ struct OpParams {
   int ag_lead_tiles;     // AllGather push pacing: an item may run this many tiles ahead of the
                          // raster group that consumes its rows (0 = unpaced)
   int ag_fanout;         // AllGather push: one item loads a row group once, stores it to all peers
+  int ag_cv_log2;        // AllGather push: 0 = an item is 4 full rows of a row-block; otherwise an
+                         // item is all rows of a row-block over a K-range of 2^ag_cv_log2 16-byte
+                         // vectors, so that consumers start on a row-block as its first range lands
   int ring_slots;        // ring depth (16-byte slots per lane) of the in-CTA exchange warp
   int use_nvls;          // exchange through NVSwitch multicast addresses when available
   int epilogue;          // Epilogue

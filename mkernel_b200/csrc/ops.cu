@@ -46,6 +46,12 @@ struct Options {
   // unpaced, 0.445 at 4..8, 0.624 at 2 which starves the consumers; W=2: 0.418 / 0.404 / 0.396).
   long long ag_lead = 6;
   long long ag_fanout = 0;   // AllGather push: load each row group once, store it to every peer
+  // AllGather push items: 1 = all rows of a row-block over one K-range (up to 32 ranges per
+  // row-block, pushed range-major), and the consumer's TMA producer waits range by range inside
+  // its K loop, so a tile starts when 1/32 of its rows' bytes have landed; 0 = 4 full rows per
+  // item and the consumer waits for the whole row-block.  The single-destination store path
+  // only: the fan-out, multicast and bulk-store variants keep the row form.
+  long long ag_chunks = 0;
   long long push_bulk = 0;   // AllGather push through TMA bulk stores instead of LSU stores
   long long ar_one_shot = 0;  // GEMM+AR: 1 = every rank reduces all rows itself (no broadcast)
   // GEMM+AR two-shot: the epilogue also stores partial rows into their owner's staging slabs
@@ -86,6 +92,7 @@ static long long* option_slot(const char* name) {
   if (!strcmp(name, "push_bulk")) return &g_opt.push_bulk;
   if (!strcmp(name, "ag_fanout")) return &g_opt.ag_fanout;
   if (!strcmp(name, "ag_lead")) return &g_opt.ag_lead;
+  if (!strcmp(name, "ag_chunks")) return &g_opt.ag_chunks;
   if (!strcmp(name, "ar_one_shot")) return &g_opt.ar_one_shot;
   if (!strcmp(name, "ar_push")) return &g_opt.ar_push;
   return nullptr;
@@ -475,6 +482,15 @@ static int run_op(const OpArgs& a, cudaStream_t stream) {
   p.push_bulk = (int)o.push_bulk;
   p.ag_fanout = (int)o.ag_fanout;
   p.ag_lead_tiles = (int)(o.ag_lead * pl.sched.group_rows * pl.sched.Q / 4);
+  if (a.op == OP_AG && a.world > 1 && o.ag_chunks != 0 && !p.push_bulk && !p.ag_fanout &&
+      !(want_nvls && a.data && a.data->mc != nullptr)) {
+    // K-range of an item: the smallest power of two of 16-byte vectors, at least one k-block
+    // (8 vectors), that covers a row in at most kGatherSub ranges.
+    const int row_vecs = a.K / 8;
+    int lg = 3;
+    while ((kGatherSub << lg) < row_vecs) ++lg;
+    p.ag_cv_log2 = lg;
+  }
   if (a.sync && a.op == OP_AR && o.ar_push != 0 && !want_nvls &&
       sync_words_needed(pl.sched) * 4 <= kArSlabByteOffset) {
     if (o.ar_push >= 2 && ar_push_fits(pl.sched, (long long)a.sync->bytes, 2)) pl.sched.ar_push = 2;

@@ -191,6 +191,22 @@ def test_allgather_fanout():
 
 
 @pytest.mark.skipif(n_gpus() < 2, reason="needs at least 2 GPUs")
+def test_allgather_k_range_items():
+    """The AllGather push in K-range form (an item is every row of a row-block over one K-range;
+    the consumer's TMA producer waits range by range inside its K loop) gives a bit-exact gathered
+    operand and the same product, ragged K and ragged row-blocks included."""
+    world = min(n_gpus(), 8)
+    world = 1 << (world.bit_length() - 1)
+    cases = [
+        dict(op="ag", M=world * 256, N=264, K=1024, seed=1, iters=2, max_rows=4096),
+        dict(op="ag", M=world * 72, N=512, K=200, seed=1, iters=2, max_rows=4096),
+        dict(op="ag", M=world * 1024, N=512, K=2048, seed=4, iters=2, max_rows=64),
+        dict(op="ag", M=8192, N=3584, K=8192, seed=6, iters=2, max_rows=16),
+    ]
+    check(launch(world, cases, options={"ag_chunks": 1}))
+
+
+@pytest.mark.skipif(n_gpus() < 2, reason="needs at least 2 GPUs")
 def test_allgather_paced_push():
     """Pacing the AllGather push against the GEMM's own progress changes timing only."""
     world = min(n_gpus(), 8)
