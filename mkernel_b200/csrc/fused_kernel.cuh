@@ -1403,6 +1403,7 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
     *s_progress = 0u;
     *s_items_done = 0u;
     s_words[5] = 0u;            // epilogue warps that have stored their rows of a tail piece
+    s_words[6] = 0u;            // set once s_epoch holds this launch's epoch
     if (!is_comm) {
       for (int i = 0; i < kMaxStages; ++i) {
         ptx::mbar_init(bar_base + 8u * (BAR_FULL + i), 1);
@@ -1437,27 +1438,44 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
   // as SMs become free (they stop at the same wait until this kernel has completed).
   ptx::grid_dependency_wait();
   ptx::grid_launch_dependents();
-  if (threadIdx.x == 0) {
-    uint32_t e = p.epoch_arg;
-    // The epoch lives on the device (graph replays need no host state) unless the caller
-    // supplies one (GEMM+AR and the multi-node style signatures pass a host epoch)
-    if (p.sync != nullptr && e == 0u) e = ptx::ld_relaxed_sys(p.sync + SW_EPOCH) + 1u;
-    *s_epoch = e;
-    if (blockIdx.x == 0) stamp(p, 0);
-    if (blockIdx.x == 0 && p.sync != nullptr && s.world > 1) {
-      // AG / RS: tell every rank that this rank has entered launch e, i.e. that its previous
-      // launch has ended and its buffers may be written again (replaces an all-rank barrier).
-      if (OP == OP_AG || OP == OP_RS)
-        for (int r = 0; r < s.world; ++r) ptx::st_release_sys(p.peer_sync[r] + SW_ENTRY + s.rank, e);
-      // AR: a rank with nothing to reduce still owes its peers the "finished" signal.
-      if (OP == OP_AR && p.n_items <= 0)
-        for (int r = 0; r < s.world; ++r) ptx::st_release_sys(p.peer_sync[r] + SW_EXIT + s.rank, e);
+  ptx::tc_fence_before();
+  __syncthreads();            // barriers initialised, tensor-memory address published
+  ptx::tc_fence_after();
+  // The launch epoch lives on the device (graph replays need no host state) unless the caller
+  // supplies one (GEMM+AR and the multi-node style signatures pass a host epoch).  Reading it is
+  // a round trip to memory, so it is kept off the path of the warps that start the GEMM: lane 0
+  // of the exchange warp reads it, and only the warps that use it (publisher, exchange and
+  // epilogue warps; everybody in an exchange CTA and in AllGather, whose TMA producer compares
+  // arrival flags with it) meet at a named barrier; the TMA producer and the MMA issuer of the
+  // other operators run on.
+  uint32_t epoch = p.epoch_arg;
+  if (p.sync != nullptr) {
+    const bool all_meet = is_comm || OP == OP_AG;
+    if (threadIdx.x == 96) {
+      uint32_t e = p.epoch_arg;
+      if (e == 0u) e = ptx::ld_relaxed_sys(p.sync + SW_EPOCH) + 1u;
+      *s_epoch = e;
+      __threadfence_block();
+      s_words[6] = 1u;          // for the warps that do not meet at the barrier below
+      if (blockIdx.x == 0) stamp(p, 0);
+      if (blockIdx.x == 0 && s.world > 1) {
+        // AG / RS: tell every rank that this rank has entered launch e, i.e. that its previous
+        // launch has ended and its buffers may be written again (replaces an all-rank barrier).
+        if (OP == OP_AG || OP == OP_RS)
+          for (int r = 0; r < s.world; ++r) ptx::st_release_sys(p.peer_sync[r] + SW_ENTRY + s.rank, e);
+        // AR: a rank with nothing to reduce still owes its peers the "finished" signal.
+        if (OP == OP_AR && p.n_items <= 0)
+          for (int r = 0; r < s.world; ++r) ptx::st_release_sys(p.peer_sync[r] + SW_EXIT + s.rank, e);
+      }
+    }
+    if (all_meet) {
+      ptx::named_barrier_sync(1, kThreads);
+      epoch = *s_epoch;
+    } else if (warp >= 2) {
+      ptx::named_barrier_sync(1, kThreads - 64);
+      epoch = *s_epoch;
     }
   }
-  ptx::tc_fence_before();
-  __syncthreads();
-  ptx::tc_fence_after();
-  const uint32_t epoch = *s_epoch;
 
   if (is_comm) {
     if (OP != OP_GEMM)
@@ -1483,6 +1501,14 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
     // ring, so every warp whose GEMM role has ended joins the exchange worker on the item queue.
     if (OP == OP_AR && s.ar_push == 2 && s.world > 1) {
       __syncwarp();
+      if (warp < 2) {
+        // the TMA producer and the MMA issuer skipped the epoch barrier: pick the epoch up now
+        const bool ok = bounded_wait<true>(wc, [&] { return s_words[6] != 0u; }, ST_TIMEOUT_PIPE,
+                                           0x700u, 0u);
+        (void)ok;   // on expiry the abort flag is up and the worker returns at its first wait
+        __threadfence_block();
+        epoch = *s_epoch;
+      }
       exchange_worker<OP, kRingInCta>(p, xchg_ring, wc, epoch, s_items_done, nullptr);
     }
   }
@@ -1508,19 +1534,34 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
     p.trace[blockIdx.x * 16 + 0] = clock64() - tr_c0;
     p.trace[blockIdx.x * 16 + 1] = global_timer_ns() - tr_t0;
   }
-  if (p.sync == nullptr || threadIdx.x != 0) return;
-  if (OP == OP_AR && s.world > 1 && *s_abort == 0u) announce_reduced_items(p, *s_items_done, epoch);
+  if (p.sync == nullptr || threadIdx.x != 96) return;   // the thread that holds the epoch
+  // AllReduce over epoch-carrying slabs: every word a peer reads from this rank carries its own
+  // epoch and every read this rank makes is local, so "this rank has finished" needs no
+  // system-scope fence and no item count -- it is the moment the last CTA gets here.  The other
+  // forms write results into the peers' outputs with plain stores and publish them through
+  // announce_reduced_items.
+  const bool ll_exit = OP == OP_AR && s.world > 1 && s.ar_push == 2;
+  if (OP == OP_AR && s.world > 1 && !ll_exit && *s_abort == 0u)
+    announce_reduced_items(p, *s_items_done, epoch);
 
-  // ---------------- exit handshake (thread 0 of every CTA) ----------------
+  // ---------------- exit handshake (one thread of every CTA) ----------------
   wc.where = (blockIdx.x << 8) | 15u;
   __threadfence();
-  const uint32_t done = atomicAdd(p.sync + SW_GRID_DONE, 1u);
-  if (done == gridDim.x - 1) {
+  // A CTA that gave up on a wait marks the count, so that the last one does not report the
+  // rank's exchange work as finished.
+  const uint32_t arrive = *s_abort == 0u ? 1u : 0x10001u;
+  const uint32_t done = atomicAdd(p.sync + SW_GRID_DONE, arrive);
+  if ((done & 0xffffu) == gridDim.x - 1) {
     // Last CTA of this rank.  AllReduce: the kernel may only end when every rank has finished
     // its exchange work (this rank's output is complete, nobody still reads its partials).
     // AG / RS need no such wait: their results are produced by this rank's own CTAs, and the
     // next launch's writers wait for the entry flag instead.
     stamp(p, 4);
+    const bool clean = ((done + arrive) >> 16) == 0u;
+    if (ll_exit && clean && p.n_items > 0) {
+      for (int r = 0; r < s.world; ++r)
+        ptx::st_relaxed_sys(p.peer_sync[r] + SW_EXIT + s.rank, epoch);
+    }
     if (OP == OP_AR && s.world > 1 && *s_abort == 0u) {
       for (int r = 0; r < s.world; ++r) {
         const uint32_t* f = p.sync + SW_EXIT + r;
@@ -1530,11 +1571,11 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
       }
     }
     stamp(p, 5);
+    // Plain stores: the end of the kernel makes them visible to the next launch.
     p.sync[SW_GRID_DONE] = 0u;
     p.sync[SW_NEXT_ITEM] = 0u;
     p.sync[SW_ITEMS_DONE] = 0u;
     p.sync[SW_EPOCH] = epoch;
-    __threadfence();
   }
 }
 

@@ -40,6 +40,11 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// bar.sync on a numbered barrier: `n_threads` (a multiple of 32) threads of the CTA meet.
+__device__ __forceinline__ void named_barrier_sync(int id, int n_threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(n_threads) : "memory");
+}
+
 // ---------------------------------------------------------------- programmatic dependent launch
 // No-ops unless the kernel was launched with the programmatic-stream-serialization attribute.
 __device__ __forceinline__ void grid_dependency_wait() {
