@@ -1535,18 +1535,19 @@ fused_gemm_kernel(const __grid_constant__ CUtensorMap tma_a,
     p.trace[blockIdx.x * 16 + 1] = global_timer_ns() - tr_t0;
   }
   if (p.sync == nullptr || threadIdx.x != 96) return;   // the thread that holds the epoch
-  // AllReduce over epoch-carrying slabs: every word a peer reads from this rank carries its own
-  // epoch and every read this rank makes is local, so "this rank has finished" needs no
-  // system-scope fence and no item count -- it is the moment the last CTA gets here.  The other
-  // forms write results into the peers' outputs with plain stores and publish them through
-  // announce_reduced_items.
+  // AllReduce over epoch-carrying slabs: items are assigned statically and every CTA passes
+  // here when its warps have finished theirs, so "this rank has finished its exchange work" is
+  // the moment the last CTA arrives below -- no separate item count.  The reduced rows went into
+  // the peers' outputs with plain stores, so every CTA still makes its own stores visible
+  // system-wide before it is counted.  The other forms publish through announce_reduced_items.
   const bool ll_exit = OP == OP_AR && s.world > 1 && s.ar_push == 2;
   if (OP == OP_AR && s.world > 1 && !ll_exit && *s_abort == 0u)
     announce_reduced_items(p, *s_items_done, epoch);
 
   // ---------------- exit handshake (one thread of every CTA) ----------------
   wc.where = (blockIdx.x << 8) | 15u;
-  __threadfence();
+  if (ll_exit) ptx::fence_acq_rel_sys();
+  else __threadfence();
   // A CTA that gave up on a wait marks the count, so that the last one does not report the
   // rank's exchange work as finished.
   const uint32_t arrive = *s_abort == 0u ? 1u : 0x10001u;
