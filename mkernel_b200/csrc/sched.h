@@ -41,9 +41,11 @@ enum OpKind : int { OP_GEMM = 0, OP_AG = 1, OP_RS = 2, OP_AR = 3 };
 enum SyncWord : int {
   SW_ENTRY = 0,       // [0,8): slot per rank: "rank s has entered launch <epoch>" (AG, RS)
   SW_EPOCH = 8,       // device-resident epoch of the last finished launch (AG, RS)
-  SW_GRID_DONE = 9,   // CTAs that reached the end of the kernel (reset by the last one)
+  SW_GRID_DONE = 9,   // CTAs that reached the end of the kernel in the low 16 bits, CTAs that
+                      // gave up on a wait above them (reset by the last CTA)
   SW_NEXT_ITEM = 10,  // next exchange work item to hand out (reset by the last CTA)
-  SW_ITEMS_DONE = 11, // exchange work items completed (reset by the last CTA)
+  SW_ITEMS_DONE = 11, // exchange work items completed, for the AllReduce forms that hand items
+                      // out through the queue (reset by the last CTA)
   SW_STATUS = 12,     // [12,16): {code, where, detail0, detail1}; 0 = healthy
   SW_EXIT = 16,       // [16,24): exit slot per rank: "rank s finished its exchange work" (AR)
   SW_FLAGS = 64,      // per-tile / per-row-group flags start here
