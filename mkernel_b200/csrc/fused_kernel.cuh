@@ -250,6 +250,7 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
     // AllGather in K-range form: vectors per range (log2) and ranges per row
     const int ag_lg = OP == OP_AG ? p.ag_cv_log2 : 0;
     const int ag_ranges = ag_lg != 0 ? ((p.K / 8) + (1 << ag_lg) - 1) >> ag_lg : 0;
+    const int ag_kb_shift = ag_lg > 3 ? ag_lg - 3 : 0;   // k-blocks per range, log2 (a range is >= 8 vectors)
     int stage = 0;
     uint32_t phase = 0;
     bool ok = true;
@@ -286,7 +287,7 @@ __device__ __forceinline__ void compute_roles(const CUtensorMap* tma_a, const CU
         int kx = w.kb0 * kBlockK;                  // element offset of the k-block
         for (int kb = w.kb0; kb < w.kb1; ++kb, kx += kBlockK) {
           if (OP == OP_AG && landed != 0xffffffffu) {
-            const int c = kb >> (ag_lg - 3);
+            const int c = kb >> ag_kb_shift;
             if (((landed >> c) & 1u) == 0u) {
               const uint32_t* f = range_flags + c;
               const long long g0 = diag_clock(tr);

@@ -363,8 +363,7 @@ static int launch_kernel(const Plan& pl, const CUtensorMap& ta, const CUtensorMa
     MKB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget));
     if (dev >= 0 && dev < 64) attr_set[dev] = true;
   }
-  cudaLaunchConfig_t cfg;
-  memset(&cfg, 0, sizeof(cfg));
+  cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(pl.grid, 1, 1);
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = pl.smem;
